@@ -1,0 +1,125 @@
+"""The CPU oracle against the fixtures that the reference's own CPU code produced
+(tests/golden/make_golden.py).  This is what pins the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.helpers import bf16_from_bits, f8_from_bits, load, moe_small_case, ref_moe_inputs
+
+
+def test_noaux_tc_topk_reference_inputs():
+    z = load("noaux_topk.npz")
+    scores = bf16_from_bits(z["ref_scores_bf16"])
+    for B in (1, 8, 16, 64, 128):      # test_noaux_tc_topk.py:191-199
+        v, i = O.noaux_tc_topk(scores.repeat(B, 1), 8, 4, 8)
+        assert torch.equal(i, torch.from_numpy(z["ref_indices"]).repeat(B, 1))
+        assert torch.equal(v.view(torch.int16), bf16_from_bits(z["ref_values_bf16"]).repeat(B, 1).view(torch.int16))
+
+
+@pytest.mark.parametrize("key,groups,keep,k", [("f32", 8, 4, 8), ("bf16", 8, 4, 8), ("g4", 4, 2, 6)])
+def test_noaux_tc_topk_more(key, groups, keep, k):
+    z = load("noaux_topk.npz")
+    sc = z[f"{key}_scores"]
+    scores = bf16_from_bits(sc) if sc.dtype == np.uint16 else torch.from_numpy(sc.copy())
+    v, i = O.noaux_tc_topk(scores, groups, keep, k)
+    assert torch.equal(i, torch.from_numpy(z[f"{key}_indices"]))
+    want = z[f"{key}_values"]
+    want = bf16_from_bits(want) if want.dtype == np.uint16 else torch.from_numpy(want.copy())
+    assert torch.equal(v.float(), want.float())
+
+
+def test_plain_topk():
+    z = load("topk.npz")
+    v, i = O.topk_lowest_index(bf16_from_bits(z["x_bf16"]), 8)
+    assert torch.equal(i.float(), torch.from_numpy(z["indices"]))
+    assert torch.equal(v.float(), torch.from_numpy(z["values"]))
+    v, i = O.topk_lowest_index(torch.from_numpy(z["x2"].copy()), 8)
+    assert torch.equal(i.float(), torch.from_numpy(z["indices2"]))
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_experts_w8a16_small_bitexact(name):
+    c = moe_small_case(name)
+    got = O.experts_w8a16(c["x"], c["ids"], c["wg"], c["wu"], c["wd"], c["sg"], c["su"], c["sd"])
+    want = c["out"]
+    m = O.parity_metrics(got, want)
+    # same statements, same dtype: expected identical; bf16 GEMM blocking may differ between
+    # batched and per-row calls, so allow one bf16 ulp on a few elements but demand near-equality
+    assert m["max_rel"] < 4e-3 and m["cosine"] > 0.99999, m
+
+
+@pytest.mark.parametrize("shape", [(1, 7168, 256, 1, 1), (1, 7168, 256, 2, 2), (1, 7168, 256, 16, 8)])
+def test_experts_w8a16_reference_shapes(shape):
+    T, H, I, E, k = shape
+    z = load("moe_ref_shapes.npz")
+    x, ids, rw, w0, w1, w2, s0, s1, s2 = ref_moe_inputs(T, H, I, E, k)
+    tag = "_".join(map(str, shape))
+    assert np.array_equal(ids.numpy(), z[f"ids_{tag}"])
+    assert abs(x.double().sum().item() - float(z[f"xsum_{tag}"])) < 1e-9, "RNG stream differs from fixture"
+    got = O.experts_w8a16(x, ids, w0, w1, w2.transpose(1, 2).contiguous(), s0, s1,
+                          s2.transpose(1, 2).contiguous())
+    want = bf16_from_bits(z[f"out_{tag}"])
+    m = O.parity_metrics(got, want)
+    assert m["max_rel"] < 4e-3 and m["cosine"] > 0.99999, m
+    # the reference's own acceptance test (test_moe.py:304-308)
+    assert m["cos_sim"] > 0.99 and m["cos_diff"] < 1e-4
+
+
+def test_dense_mlp_matches_reference():
+    z = load("mlp_dense.npz")
+    x = bf16_from_bits(z["x"])
+    wg, wu, wd = f8_from_bits(z["wg"]), f8_from_bits(z["wu"]), f8_from_bits(z["wd"])
+    sg, su, sd = bf16_from_bits(z["sg"]), bf16_from_bits(z["su"]), bf16_from_bits(z["sd"])
+    got = O.expert_mlp_w8a16(x, wg, wu, wd.t().contiguous(), sg, su, sd.t().contiguous())
+    m = O.parity_metrics(got.float().flatten(), torch.from_numpy(z["out"].copy()))
+    assert m["max_rel"] < 4e-3 and m["cosine"] > 0.99999, m
+
+
+def test_w8a8_oracle_close_to_w8a16_but_not_within_tolerance_by_construction():
+    """W8A8 (oracle-B) vs W8A16 (oracle-A): close (reference's own acceptance test passes) -
+    documents why the FP8 kernels are compared with oracle-B."""
+    c = moe_small_case("a")
+    # positive fp32 scales as the benchmark configurations use
+    a = O.experts_w8a16(c["x"], c["ids"], c["wg"], c["wu"], c["wd"], c["sg"], c["su"], c["sd"])
+    b = O.experts_w8a8(c["x"], c["ids"], c["wg"], c["wu"], c["wd"], c["sg"].float(), c["su"].float(),
+                       c["sd"].float())
+    m = O.parity_metrics(b, a)
+    assert m["cos_sim"] > 0.99 and m["cosine"] > 0.995, m
+
+
+def test_permutation_matches_reference_nonzero_form():
+    g = torch.Generator().manual_seed(3)
+    T, k, E = 37, 4, 16
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    order, offs = O.permutation(ids, E)
+    gather, scatter, cnt = O.gather_scatter_index(ids, E)
+    for e in range(E):
+        seg = order[offs[e]:offs[e + 1]]
+        assert torch.equal(seg, scatter[e, :cnt[e]])
+        assert torch.equal(seg // k, gather[e, :cnt[e]])
+    assert int(offs[-1]) == T * k
+
+
+def test_quant_act_roundtrip_and_edges():
+    x = torch.zeros(3, 256)
+    x[1, :128] = torch.linspace(-5, 5, 128)
+    x[2, 128:] = 1e-20
+    q, s = O.quant_act_1x128(x)
+    d = O.dequant_act(q, s)
+    assert torch.isfinite(d).all() and torch.isfinite(s).all()
+    assert d[0].abs().max() == 0
+    assert (d[1, :128] - x[1, :128]).abs().max() <= 5 / 448 * 16 + 1e-6   # <= half an e4m3 step at the top binade
+    assert q.float().abs().max() <= 448
+
+
+def test_route_oracles_basic():
+    x, wr, logits = O.make_inputs(32, 256, 64, seed=1)
+    ids, w = O.route_softmax_topk(logits, 4)
+    assert ids.dtype == torch.int32 and torch.allclose(w.sum(-1), torch.ones(32), atol=1e-6)
+    bias = torch.randn(64) * 0.01
+    ids2, w2 = O.route_sigmoid_grouped(logits, bias, 8, 4, 6, 2.5)
+    assert torch.allclose(w2.sum(-1), torch.full((32,), 2.5), atol=1e-5)
+    assert ((ids2 // 8).unique(dim=-1).shape[-1]) <= 6
+    for r in range(32):
+        assert len(set((ids2[r] // 8).tolist())) <= 4
