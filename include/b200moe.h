@@ -1,0 +1,164 @@
+/* b200moe.h - C ABI of the B200 (sm_100a) fused-MoE kernels.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless stated otherwise, every
+ * call enqueues work on `stream` (a cudaStream_t passed as void*) of the CURRENT device and returns
+ * without synchronising.  Nothing here allocates device memory: the caller owns inputs, outputs and
+ * the workspace (size from b200moe_experts_workspace_bytes).
+ *
+ * Return value: 0 = enqueued; negative = argument rejected on the host before any launch
+ * (B200MOE_E*); positive = the cudaError_t of a failed launch.
+ *
+ * These entry points are what the reference's vendor C ABI (third_party/tpuDNN/include/tpuDNN.h:6-48,
+ * tpuDNNTensor.h) is to its op wrappers in torch_tpu/csrc/ops/my_ops/: each one names the reference
+ * interface it stands in for.
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200MOE_ABI_VERSION 1
+
+enum {
+  B200MOE_OK = 0,
+  B200MOE_EINVAL = -1,     /* null pointer, non-positive size, unknown enum */
+  B200MOE_ESHAPE = -2,     /* a size the kernels do not support (see each call) */
+  B200MOE_EWORKSPACE = -3, /* workspace too small or misaligned */
+  B200MOE_EALIGN = -4,     /* a pointer that must be 16-byte aligned is not */
+  B200MOE_EDRIVER = -5     /* the CUDA driver entry point for tensor maps is unavailable */
+};
+
+/* element types of score / scale / weight tensors */
+enum { B200MOE_F32 = 0, B200MOE_BF16 = 1, B200MOE_F16 = 2 };
+
+/* score functions of b200moe_route */
+enum { B200MOE_SCORE_SOFTMAX = 0, B200MOE_SCORE_SIGMOID = 1 };
+
+/* output modes of b200moe_experts */
+enum {
+  B200MOE_OUT_PER_SLOT = 0, /* out [T,k,H] bf16, un-weighted (what the reference op returns) */
+  B200MOE_OUT_COMBINED = 1  /* out [T,H] bf16 = sum_j w[t,j] * y[t,j,:] (+ shared expert)     */
+};
+
+/* arithmetic of the expert GEMMs */
+enum {
+  B200MOE_ACT_W8A8 = 0,  /* activations quantised per token per 128 columns to e4m3; FP8 tensor cores */
+  B200MOE_ACT_W8A16 = 1  /* reference arithmetic: weights dequantised to bf16, bf16 roundings kept   */
+};
+
+/* kernel family selector (tests use it to A/B the two implementations) */
+enum { B200MOE_IMPL_AUTO = 0, B200MOE_IMPL_SIMPLE = 1, B200MOE_IMPL_TCGEN05 = 2 };
+
+int b200moe_abi_version(void);
+const char* b200moe_error_string(int code);
+
+/* Device-side status word of the last kernels that ran with `status` != NULL: 0 = ok, bit 0 = an
+ * expert id outside [0,E) was skipped, bit 1 = a bounded wait inside a kernel gave up. */
+
+/* ---- routing -------------------------------------------------------------------------------- */
+
+/* Grouped top-k on given scores.  Stands in for tpudnnNoauxTcTopkAsync
+ * (third_party/tpuDNN/include/tpuDNNTensor.h:728-737; wrapper my_ops/NoauxTcTopk.cpp:9-67).
+ * scores [batch, n_experts] of `dtype`; values [batch, top_k] of the same dtype; indices int32.
+ * Group score = sum of the group's two largest scores, formed in `dtype`; ties -> lowest index.
+ * Limits: n_experts <= 1024, n_groups <= 32, top_k <= 32. */
+int b200moe_noaux_tc_topk(void* values, int32_t* indices, const void* scores, int dtype,
+                          int64_t batch, int64_t n_experts, int64_t n_groups, int64_t topk_groups,
+                          int64_t top_k, void* stream);
+
+/* Plain descending top-k along the last dim, int32 indices.  Stands in for tpudnnTopkAsync as used by
+ * aten::topk on the device (native_ops/Topk.cpp:90-150).  n <= 1024, k <= 32. */
+int b200moe_topk(void* values, int32_t* indices, const void* x, int dtype, int64_t batch, int64_t n,
+                 int64_t k, void* stream);
+
+/* Router GEMM: logits[T,E] (fp32) = x[T,H] (bf16) . wr[E,H]^T (bf16).  First op of the caller-side
+ * routing chain (python/regression/test_llm/test_torch_ops.py:439-455).  H % 8 == 0. */
+int b200moe_router_logits(float* logits, const void* x, const void* wr, int64_t T, int64_t H,
+                          int64_t E, void* stream);
+
+/* The rest of that chain in one kernel: score (softmax | sigmoid) -> (+bias, selection only) ->
+ * group-limited top-k -> gather un-biased scores -> optional renormalisation -> * scale.
+ * logits fp32 [T,E]; bias fp32 [E] or NULL; ids int32 [T,k]; w fp32 [T,k]; w_bf16 (optional) bf16
+ * [T,k].  n_groups <= 1 disables grouping.  Also the arithmetic behind
+ * tpudnnFusedMoEGroupedTopkMultiCoreAsync (tpuDNNTensor.h:1572-1583). */
+int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits, const float* bias,
+                  int64_t T, int64_t E, int64_t k, int score_func, int64_t n_groups,
+                  int64_t topk_groups, int renorm, float scale, void* stream);
+
+/* ---- permutation ------------------------------------------------------------------------------ */
+
+/* Stable sort of the T*k (token,slot) pairs by expert id: sorted_pair[P] (flat t*k+j, ascending
+ * inside an expert), expert_offsets[E+1].  The device twin of phases 1-2 of the reference kernel
+ * (my_ops/fusedMoE.pl:624-756).  scratch: int32[b200moe_permute_scratch_ints(P,E)].
+ * Ids outside [0,E) are dropped (status bit 0). */
+size_t b200moe_permute_scratch_ints(int64_t P, int64_t E);
+int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
+                    int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream);
+
+/* The reference's own scratch layout (fusedMoE.cpp:303-306, fusedMoE.pl:737-755): gather_index[E,T]
+ * (token ids), scatter_index[E,T] (flat pair ids), num_per_expert[E]; unused tail entries are left
+ * untouched.  Computed from sorted_pair / expert_offsets. */
+int b200moe_gather_scatter_index(int32_t* gather_index, int32_t* scatter_index,
+                                 int32_t* num_per_expert, const int32_t* sorted_pair,
+                                 const int32_t* expert_offsets, int64_t T, int64_t k, int64_t E,
+                                 void* stream);
+
+/* Row gather + per-row 1x128 e4m3 quantisation: for r in [0,rows): src = row_map ? row_map[r]/div : r;
+ * q[r,:] = e4m3(x[src,:] * 448/amax), s_t[g, r] = amax/448 (scales stored group-major, [H/128, ld]).
+ * x bf16 [*,H]; H % 128 == 0. */
+int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void* x, const int32_t* row_map,
+                       int64_t div, int64_t rows, int64_t H, void* stream);
+
+/* ---- experts ------------------------------------------------------------------------------------ */
+
+/* Everything after routing: permute -> quantise -> grouped gate/up GEMM + SiLU*up (+ requantise) ->
+ * grouped down GEMM -> scatter (per-slot) or weighted combine.  Stands in for
+ * tpudnnFusedMoEFusedExpertsMultiCoreAsync (tpuDNNTensor.h:1585-1611; wrapper my_ops/fusedMoE.cpp:117-236)
+ * and for the PPL kernel behind fused_moe_fused_experts_v2 (my_ops/fusedMoE.pl:795-810).
+ *
+ *   x        bf16 [T,H]
+ *   w_gate, w_up, w_down   e4m3 [E,I,H]  (down = W_down^T, contiguous: test_moe.py:285)
+ *   s_gate, s_up, s_down   [E, I/128, H/128] of scale_dtype (fp32 or bf16); NULL with
+ *                          scale_dtype = -1 is not supported here (bf16 weights are out of scope)
+ *   ids      int32 [T,k];  topk_w  [T,k] of w_dtype (needed for B200MOE_OUT_COMBINED, else may be NULL)
+ *   shared_* optional dense expert applied to every token with weight 1 (combined mode only), same
+ *            layouts with E = 1 and intermediate size I_shared; pass NULL / 0 to disable
+ *   out      bf16 [T,k,H] or [T,H] by out_mode
+ *   workspace  >= b200moe_experts_workspace_bytes(...) bytes, 256-byte aligned
+ *   status   optional int32 device word (see above)
+ * H % 128 == 0, I % 128 == 0, T*k < 2^24.  */
+typedef struct {
+  int64_t T, H, I, E, k;
+  int64_t I_shared;   /* 0 = no shared expert */
+  int out_mode;       /* B200MOE_OUT_* */
+  int act_mode;       /* B200MOE_ACT_* */
+  int impl;           /* B200MOE_IMPL_* */
+  int scale_dtype;    /* B200MOE_F32 | B200MOE_BF16 */
+  int w_dtype;        /* dtype of topk_w: B200MOE_F32 | B200MOE_BF16 */
+  int reserved;       /* 0; tests: bits 0-1 / 2-3 force the gate-up / down GEMM to 1 = simple, 2 = tcgen05 */
+} b200moe_experts_desc;
+
+size_t b200moe_experts_workspace_bytes(const b200moe_experts_desc* d);
+
+int b200moe_experts(void* out, const void* x, const void* w_gate, const void* w_up,
+                    const void* w_down, const void* s_gate, const void* s_up, const void* s_down,
+                    const int32_t* ids, const void* topk_w, const void* shared_w_gate,
+                    const void* shared_w_up, const void* shared_w_down, const void* shared_s_gate,
+                    const void* shared_s_up, const void* shared_s_down,
+                    const b200moe_experts_desc* d, void* workspace, size_t workspace_bytes,
+                    int32_t* status, void* stream);
+
+/* Weighted combine on its own (the caller-side bmm of python/regression/test_llm/test_bmm.py:118-134):
+ * out[t,:] = bf16( sum_j w[t,j] * y[t,j,:] (+ add[t,:]) ), fp32 accumulation. */
+int b200moe_combine(void* out, const void* y, const void* w, int w_dtype, const void* add, int64_t T,
+                    int64_t k, int64_t H, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

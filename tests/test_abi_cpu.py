@@ -1,0 +1,74 @@
+"""No-GPU checks of the boundary: the C-ABI library loads and exports every symbol include/b200moe.h declares,
+the op library registers the reference's op names with the reference's schemas, host-side argument checks run
+before any launch, and the workspace size function behaves."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def m():
+    import torch_tpu_b200
+    if not os.path.exists(torch_tpu_b200.lib.LIB_PATH) or not os.path.exists(torch_tpu_b200.OPS_LIB_PATH):
+        from importlib import import_module
+        import_module("torch_tpu_b200.build").build_all()
+    return torch_tpu_b200
+
+
+def test_every_declared_symbol_is_exported(m):
+    header = open(os.path.join(ROOT, "include", "b200moe.h")).read()
+    declared = set(re.findall(r"\b(b200moe_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    l = m.lib.lib()
+    for name in sorted(declared):
+        assert hasattr(l, name), f"{name} declared in include/b200moe.h but not exported"
+    assert declared == set(m.lib.SIGNATURES), "ctypes binding and header disagree"
+    assert l.b200moe_abi_version() == 1
+    assert b"workspace" in l.b200moe_error_string(-3)
+
+
+def test_host_side_rejections_need_no_gpu(m):
+    l = m.lib.lib()
+    null = ctypes.c_void_p(0)
+    assert l.b200moe_topk(null, null, null, 0, 1, 8, 2, null) == m.lib.EINVAL
+    one = ctypes.c_void_p(16)
+    assert l.b200moe_topk(one, one, one, 0, 1, 2048, 2, null) == m.lib.ESHAPE
+    assert l.b200moe_noaux_tc_topk(one, one, one, 0, 1, 256, 7, 4, 8, null) == m.lib.ESHAPE
+    assert l.b200moe_quant_rows(one, one, 128, one, null, 1, 4, 100, null) == m.lib.ESHAPE
+    assert l.b200moe_combine(one, one, one, 0, null, 4, 2, 12, null) == m.lib.ESHAPE
+    assert l.b200moe_combine(ctypes.c_void_p(8), one, one, 0, null, 4, 2, 16, null) == m.lib.EALIGN
+
+
+def test_workspace_bytes(m):
+    ops = m.ops
+    d = ops.make_desc(4096, 4096, 14336, 8, 2, out_mode=m.lib.OUT_COMBINED)
+    n = ops.experts_workspace_bytes(d)
+    P = 8192
+    assert n >= P * 4096 + P * 14336 + P * 4096 * 2
+    assert n < 2 * (P * 4096 + P * 14336 + P * 4096 * 2)
+    assert ops.experts_workspace_bytes(ops.make_desc(4, 100, 128, 4, 2)) == 0       # H % 128 != 0
+    d2 = ops.make_desc(16, 7168, 2048, 256, 8, I_shared=2048, out_mode=m.lib.OUT_COMBINED)
+    assert ops.experts_workspace_bytes(d2) > ops.experts_workspace_bytes(
+        ops.make_desc(16, 7168, 2048, 256, 8, out_mode=m.lib.OUT_COMBINED))
+
+
+def test_op_surface_matches_reference_names_and_schemas(m):
+    m.load_ops()
+    want = {
+        "fused_moe_fused_experts": 25, "fused_moe_fused_experts_v2": 27, "fused_moe_grouped_topk": 10,
+        "noaux_tc_topk": 6, "mlp_w8a16_dq_forward": 9, "mlp_w8a8_quant_forward": 9}
+    for name, nargs in want.items():
+        op = getattr(torch.ops.my_ops, name)
+        schema = op.default._schema
+        assert len(schema.arguments) == nargs, (name, str(schema))
+    s = str(torch.ops.my_ops.fused_moe_fused_experts.default._schema)
+    # Tensor output, input, Tensor? x2, 3 weights, 3 optional scales, ids, weights, 3 optionals, 3 ints, bool, 2 ints,
+    # 3 optionals, bool (torch_tpu/csrc/ops/my_ops/fusedMoE.cpp:117-130)
+    assert s.count("Tensor?") == 11 and s.count("int ") == 5 and s.count("bool ") == 2, s
+    with pytest.raises(RuntimeError, match="CUDA"):
+        torch.ops.my_ops.noaux_tc_topk(torch.zeros(1, 8), torch.zeros(1, 8, dtype=torch.int32), torch.zeros(1, 256), 8, 4, 8)

@@ -1,0 +1,150 @@
+"""The reference-facing surface: torch.ops.my_ops.* called the way the reference's own tests call them
+(python/regression/test_llm/test_moe.py:119-140, test_noaux_tc_topk.py:99-110), and the FusedMoE layer."""
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+from tests.gpu_util import small_problem, to_dev
+from tests.helpers import bf16_from_bits, f8_from_bits, load, moe_small_case
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def m():
+    import torch_tpu_b200
+    torch_tpu_b200.load_ops()
+    return torch_tpu_b200
+
+
+def test_op_noaux_tc_topk_like_reference_test(m):
+    z = load("noaux_topk.npz")
+    scores = bf16_from_bits(z["ref_scores_bf16"]).repeat(16, 1)
+    values = torch.empty(16, 8, dtype=scores.dtype).to(DEV)
+    indices = torch.empty(16, 8, dtype=torch.int32).to(DEV)
+    torch.ops.my_ops.noaux_tc_topk(values, indices, scores.clone().to(DEV), 8, 4, 8)
+    vg, ig = O.noaux_tc_topk(scores, 8, 4, 8)
+    assert torch.allclose(vg.float(), values.cpu().float(), rtol=1e-5, atol=1e-6)
+    assert torch.equal(ig, indices.cpu().long())
+    with pytest.raises(RuntimeError):  # dtype mismatch, as my_ops/NoauxTcTopk.cpp:24-26
+        torch.ops.my_ops.noaux_tc_topk(values.float(), indices, scores.to(DEV), 8, 4, 8)
+    with pytest.raises(RuntimeError):  # CPU tensors are rejected, there is no CPU path
+        torch.ops.my_ops.noaux_tc_topk(values.cpu(), indices.cpu(), scores, 8, 4, 8)
+
+
+def _call_v1(out, d, E, k):
+    return torch.ops.my_ops.fused_moe_fused_experts(
+        out, d["x"], None, None, d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"], d["rw"],
+        None, None, None, 128, E, k, True, 8, 4, None, None, None, False)
+
+
+def test_op_fused_experts_per_slot_and_combined(m):
+    T, H, I, E, k = 48, 512, 256, 8, 2
+    p = small_problem(T, H, I, E, k, seed=11)
+    p["rw"] = p["w"].to(torch.bfloat16)
+    d = to_dev(p)
+    want = O.experts_w8a8(p["x"], p["ids"], p["wg"], p["wu"], p["wd"], p["sg"], p["su"], p["sd"])
+    out = torch.empty(T, k, H, dtype=torch.bfloat16, device=DEV)
+    r = _call_v1(out, d, E, k)
+    assert r.data_ptr() == out.data_ptr()          # returns the output it was given (my_ops/fusedMoE.cpp:235)
+    met = O.parity_metrics(out, want)
+    assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+    out2 = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    _call_v1(out2, d, E, k)
+    want2 = (want.float() * p["rw"].float()[..., None]).sum(1)
+    met = O.parity_metrics(out2, want2)
+    assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+    # v2 with the reference's scratch tensors (test_moe.py:289-295)
+    sem = torch.empty(E, T, dtype=torch.int32, device=DEV)
+    out3 = torch.empty(T, k, H, dtype=torch.bfloat16, device=DEV)
+    torch.ops.my_ops.fused_moe_fused_experts_v2(
+        out3, d["x"], None, None, d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"], d["rw"], None,
+        sem, sem.clone(), sem.clone(), torch.empty(E, T, k, dtype=torch.int32, device=DEV), 128, E, k, True, 8, 4,
+        None, None, None, False)
+    assert torch.equal(out3, out)
+
+
+def test_op_argument_checks(m):
+    p = small_problem(4, 256, 128, 4, 2)
+    p["rw"] = p["w"].to(torch.bfloat16)
+    d = to_dev(p)
+    out = torch.empty(4, 2, 256, dtype=torch.bfloat16, device=DEV)
+    bad = dict(d)
+    bad["ids"] = d["ids"].long()
+    with pytest.raises(RuntimeError, match="int32"):   # my_ops/fusedMoE.cpp:143-144
+        _call_v1(out, bad, 4, 2)
+    with pytest.raises(RuntimeError):
+        torch.ops.my_ops.fused_moe_fused_experts(
+            out, d["x"], None, None, d["wg"], d["wu"], d["wd"], None, None, None, d["ids"], d["rw"], None, None,
+            None, 128, 4, 2, True, 8, 4, None, None, None, False)
+
+
+def test_op_dense_mlp_w8a16_matches_reference_golden(m):
+    z = load("mlp_dense.npz")
+    x = bf16_from_bits(z["x"])
+    wg, wu, wd = f8_from_bits(z["wg"]), f8_from_bits(z["wu"]), f8_from_bits(z["wd"])
+    sg, su, sd = bf16_from_bits(z["sg"]), bf16_from_bits(z["su"]), bf16_from_bits(z["sd"])
+    out = torch.empty(x.shape, dtype=torch.bfloat16, device=DEV)
+    torch.ops.my_ops.mlp_w8a16_dq_forward(x.to(DEV), wg.to(DEV), wu.to(DEV), wd.t().contiguous().to(DEV),
+                                          sg.to(DEV), su.to(DEV), sd.t().contiguous().to(DEV), out, 128)
+    met = O.parity_metrics(out.float().flatten(), torch.from_numpy(z["out"].copy()))
+    assert met["cos_sim"] >= 0.99 and met["max_rel"] <= 2e-2, met     # test_mlp_w8a16_dq.py:219-220
+    out8 = torch.empty_like(out)
+    torch.ops.my_ops.mlp_w8a8_quant_forward(x.to(DEV), wg.to(DEV), wu.to(DEV), wd.t().contiguous().to(DEV),
+                                            sg.to(DEV), su.to(DEV), sd.t().contiguous().to(DEV), out8, 128)
+    met = O.parity_metrics(out8.float().flatten(), torch.from_numpy(z["out"].copy()))
+    assert met["cos_sim"] >= 0.99, met
+
+
+def test_op_fused_moe_grouped_topk(m):
+    T, H, E, k = 33, 512, 64, 4
+    x, wr, _ = O.make_inputs(T, H, E, seed=2, router_std=0.2)
+    ids = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    w32 = torch.empty(T, k, dtype=torch.float32, device=DEV)
+    w16 = torch.empty(T, k, dtype=torch.bfloat16, device=DEV)
+    mm = torch.empty(T, E, dtype=torch.float32, device=DEV)
+    sm = torch.empty(T, E, dtype=torch.float32, device=DEV)
+    mx = torch.empty(T, dtype=torch.float32, device=DEV)
+    xl, wl = x.to(DEV), wr.to(DEV)
+    torch.ops.my_ops.fused_moe_grouped_topk(ids, w16, xl, wl, w32, xl.float(), wl.float(), mx, mm, sm)
+    O.assert_tie_free(torch.softmax(mm.cpu(), -1), k)
+    wid, ww = O.route_softmax_topk(mm.cpu(), k)
+    assert torch.equal(ids.cpu(), wid)
+    torch.testing.assert_close(w32.cpu(), ww, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("cfgname", ["mixtral_like", "deepseek_like"])
+def test_layer_end_to_end(m, cfgname):
+    from torch_tpu_b200.layer import FusedMoE, MoEConfig
+    if cfgname == "mixtral_like":
+        cfg = MoEConfig(512, 256, 8, 2)
+        bias, shared = None, None
+    else:
+        cfg = MoEConfig(512, 256, 64, 6, "sigmoid", 8, 4, True, 2.5, shared_intermediate=256)
+        bias = torch.randn(64, generator=torch.Generator().manual_seed(1)) * 0.01
+        shared = O.make_expert_weights(1, 512, 256, seed=77)
+    T = 80
+    p = small_problem(T, cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, seed=21)
+    x, wr, _ = O.make_inputs(T, cfg.hidden, cfg.num_experts, seed=21, router_std=0.2)
+    layer = FusedMoE(cfg, wr.to(DEV), *(p[n].to(DEV) for n in ("wg", "wu", "wd", "sg", "su", "sd")),
+                     bias=bias.to(DEV) if bias is not None else None,
+                     shared=tuple(t.to(DEV) for t in shared) if shared else None, max_tokens=128)
+    y = layer(x.to(DEV))
+    ids, w = layer.ids[:T].cpu(), layer.topk_w[:T].cpu()
+    lg = layer.logits[:T].cpu()
+    if cfgname == "mixtral_like":
+        wid, ww = O.route_softmax_topk(lg, cfg.top_k)
+    else:
+        wid, ww = O.route_sigmoid_grouped(lg, bias, 8, 4, cfg.top_k, 2.5)
+    assert torch.equal(ids, wid)
+    want = O.moe_layer_w8a8(x, wid, tuple(p[n] for n in ("wg", "wu", "wd", "sg", "su", "sd")),
+                            shared=tuple(t[0] for t in shared) if shared else None, topk_w=w)
+    met = O.parity_metrics(y, want)
+    assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+    assert int(layer.status.item()) == 0
+    # host-buffer entry point
+    xh, oh = x.pin_memory(), torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()
+    layer.forward_host(xh, oh)
+    torch.cuda.synchronize()
+    assert torch.equal(oh, y.cpu())

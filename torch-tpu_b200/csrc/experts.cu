@@ -1,0 +1,229 @@
+// The expert pipeline behind b200moe_experts: permute -> (quantise) -> grouped gate/up GEMM with SiLU*up
+// -> grouped down GEMM -> scatter or weighted combine, all enqueued on one stream into a caller-owned
+// workspace.  Stands in for tpudnnFusedMoEFusedExpertsMultiCoreAsync
+// (third_party/tpuDNN/include/tpuDNNTensor.h:1585-1611) and the PPL kernel my_ops/fusedMoE.pl:795-810.
+#include "internal.h"
+
+namespace {
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct WsLayout {
+  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y;
+  size_t s_offsets, s_mtiles, s_nmt, s_xq, s_xs, s_hq, s_hs, s_y;
+  size_t total;
+  int64_t P, ld, lds;
+  int max_mtiles, s_max_mtiles;
+};
+
+WsLayout make_layout(const b200moe_experts_desc& d) {
+  WsLayout L{};
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = o;
+    o = align_up(o + bytes, 256);
+    return at;
+  };
+  const int64_t P = d.T * d.k;
+  L.P = P;
+  L.ld = (int64_t)align_up((size_t)P, kTileM);
+  L.lds = (int64_t)align_up((size_t)d.T, kTileM);
+  L.max_mtiles = (int)(P / kTileM + d.E);
+  L.s_max_mtiles = (int)((d.T + kTileM - 1) / kTileM);
+  const bool w8a8 = d.act_mode == B200MOE_ACT_W8A8;
+  const size_t nH = d.H / kBlock, nI = d.I / kBlock;
+  L.offsets = take((d.E + 1) * sizeof(int32_t));
+  L.sorted = take((size_t)P * sizeof(int32_t));
+  L.scratch = take(b200moe_permute_scratch_ints(P, d.E) * sizeof(int32_t));
+  L.mtiles = take((size_t)L.max_mtiles * 2 * sizeof(int32_t));
+  L.nmt = take(sizeof(int32_t));
+  L.xq = take(w8a8 ? (size_t)P * d.H : 0);
+  L.xs = take(w8a8 ? nH * (size_t)L.ld * sizeof(float) : 0);
+  L.hq = take(w8a8 ? (size_t)P * d.I : (size_t)P * d.I * 2);
+  L.hs = take(w8a8 ? nI * (size_t)L.ld * sizeof(float) : 0);
+  L.y = take(d.out_mode == B200MOE_OUT_COMBINED ? (size_t)P * d.H * 2 : 0);
+  if (d.I_shared > 0) {
+    const size_t nIs = d.I_shared / kBlock;
+    L.s_offsets = take(2 * sizeof(int32_t));
+    L.s_mtiles = take((size_t)L.s_max_mtiles * 2 * sizeof(int32_t));
+    L.s_nmt = take(sizeof(int32_t));
+    L.s_xq = take(w8a8 ? (size_t)d.T * d.H : 0);
+    L.s_xs = take(w8a8 ? nH * (size_t)L.lds * sizeof(float) : 0);
+    L.s_hq = take(w8a8 ? (size_t)d.T * d.I_shared : (size_t)d.T * d.I_shared * 2);
+    L.s_hs = take(w8a8 ? nIs * (size_t)L.lds * sizeof(float) : 0);
+    L.s_y = take((size_t)d.T * d.H * 2);
+  }
+  L.total = o;
+  return L;
+}
+
+int check_desc(const b200moe_experts_desc* d) {
+  MOE_CHECK_ARG(d);
+  MOE_CHECK_ARG(d->T >= 0 && d->H > 0 && d->I > 0 && d->E > 0 && d->k > 0 && d->I_shared >= 0);
+  MOE_CHECK_ARG(d->out_mode == B200MOE_OUT_PER_SLOT || d->out_mode == B200MOE_OUT_COMBINED);
+  MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8 || d->act_mode == B200MOE_ACT_W8A16);
+  MOE_CHECK_ARG(d->impl >= B200MOE_IMPL_AUTO && d->impl <= B200MOE_IMPL_TCGEN05);
+  MOE_CHECK_ARG(d->scale_dtype == B200MOE_F32 || d->scale_dtype == B200MOE_BF16);
+  MOE_CHECK_ARG(d->w_dtype == B200MOE_F32 || d->w_dtype == B200MOE_BF16);
+  MOE_CHECK_SHAPE(d->H % kBlock == 0 && d->I % kBlock == 0 && d->I_shared % kBlock == 0);
+  MOE_CHECK_SHAPE(d->E <= 1024 && d->T * d->k < (1 << 24));
+  MOE_CHECK_SHAPE(d->H < (1 << 24) && d->I < (1 << 24) && d->E * d->I < (int64_t(1) << 31));
+  if (d->I_shared > 0) MOE_CHECK_ARG(d->out_mode == B200MOE_OUT_COMBINED);
+  if (d->impl == B200MOE_IMPL_TCGEN05) MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8);
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+extern "C" size_t b200moe_experts_workspace_bytes(const b200moe_experts_desc* d) {
+  if (check_desc(d) != B200MOE_OK) return 0;
+  return make_layout(*d).total;
+}
+
+extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, const void* w_up,
+                               const void* w_down, const void* s_gate, const void* s_up, const void* s_down,
+                               const int32_t* ids, const void* topk_w, const void* shared_w_gate,
+                               const void* shared_w_up, const void* shared_w_down,
+                               const void* shared_s_gate, const void* shared_s_up,
+                               const void* shared_s_down, const b200moe_experts_desc* d, void* workspace,
+                               size_t workspace_bytes, int32_t* status, void* stream) {
+  int rc = check_desc(d);
+  if (rc != B200MOE_OK) return rc;
+  MOE_CHECK_ARG(out && x && w_gate && w_up && w_down && s_gate && s_up && s_down && ids);
+  if (d->out_mode == B200MOE_OUT_COMBINED) MOE_CHECK_ARG(topk_w);
+  if (d->I_shared > 0)
+    MOE_CHECK_ARG(shared_w_gate && shared_w_up && shared_w_down && shared_s_gate && shared_s_up && shared_s_down);
+  if (!moe_aligned16(out) || !moe_aligned16(x) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
+      !moe_aligned16(w_down))
+    return B200MOE_EALIGN;
+  if (d->T == 0) return B200MOE_OK;
+  const WsLayout L = make_layout(*d);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return B200MOE_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = reinterpret_cast<char*>(workspace);
+  auto I32 = [&](size_t off) { return reinterpret_cast<int32_t*>(ws + off); };
+  const bool w8a8 = d->act_mode == B200MOE_ACT_W8A8;
+  const bool use_tc = w8a8 && d->impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
+  if (d->impl == B200MOE_IMPL_TCGEN05 && !use_tc) return B200MOE_EDRIVER;
+  const bool combined = d->out_mode == B200MOE_OUT_COMBINED;
+  // per-GEMM override for A/B tests: reserved bits 0-1 (gate/up GEMM) and 2-3 (down GEMM): 1 = simple, 2 = tcgen05
+  const int o1 = d->reserved & 3, o2 = (d->reserved >> 2) & 3;
+  const bool tc1 = w8a8 && moe_tc_available() && (o1 ? o1 == 2 : use_tc);
+  const bool tc2 = w8a8 && moe_tc_available() && (o2 ? o2 == 2 : use_tc);
+
+  rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
+  if (rc) return rc;
+  rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, st);
+  if (rc) return rc;
+  if (w8a8) {
+    rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.xq), reinterpret_cast<float*>(ws + L.xs), L.ld,
+                            x, I32(L.sorted), d->k, L.P, d->H, stream);
+    if (rc) return rc;
+  }
+
+  MoeGemmArgs g{};
+  g.aq = reinterpret_cast<const uint8_t*>(ws + L.xq);
+  g.as_t = reinterpret_cast<const float*>(ws + L.xs);
+  g.ld = L.ld;
+  g.a16 = reinterpret_cast<const __nv_bfloat16*>(x);
+  g.row_map = I32(L.sorted);
+  g.div = (int)d->k;
+  g.w0 = reinterpret_cast<const uint8_t*>(w_gate);
+  g.w1 = reinterpret_cast<const uint8_t*>(w_up);
+  g.s0 = s_gate;
+  g.s1 = s_up;
+  g.scale_dtype = d->scale_dtype;
+  g.mtiles = I32(L.mtiles);
+  g.num_mtiles = I32(L.nmt);
+  g.offsets = I32(L.offsets);
+  g.max_mtiles = L.max_mtiles;
+  g.P = L.P;
+  g.H = (int)d->H;
+  g.I = (int)d->I;
+  g.E = (int)d->E;
+  g.hq = reinterpret_cast<uint8_t*>(ws + L.hq);
+  g.hs_t = reinterpret_cast<float*>(ws + L.hs);
+  g.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.hq);
+  g.status = status;
+  rc = tc1 ? moe_gemm1_tc(g, st) : moe_gemm1_simple(g, d->act_mode, st);
+  if (rc) return rc;
+
+  MoeGemmArgs g2 = g;
+  g2.aq = g.hq;
+  g2.as_t = g.hs_t;
+  g2.a16 = g.h16;
+  g2.w0 = reinterpret_cast<const uint8_t*>(w_down);
+  g2.w1 = nullptr;
+  g2.s0 = s_down;
+  g2.s1 = nullptr;
+  g2.out = reinterpret_cast<__nv_bfloat16*>(combined ? (void*)(ws + L.y) : out);
+  rc = tc2 ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, d->act_mode, st);
+  if (rc) return rc;
+
+  const void* add = nullptr;
+  if (d->I_shared > 0) {
+    rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, st);
+    if (rc) return rc;
+    rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, st);
+    if (rc) return rc;
+    if (w8a8) {
+      rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.s_xq), reinterpret_cast<float*>(ws + L.s_xs),
+                              L.lds, x, nullptr, 1, d->T, d->H, stream);
+      if (rc) return rc;
+    }
+    MoeGemmArgs s = g;
+    s.aq = reinterpret_cast<const uint8_t*>(ws + L.s_xq);
+    s.as_t = reinterpret_cast<const float*>(ws + L.s_xs);
+    s.ld = L.lds;
+    s.row_map = nullptr;
+    s.div = 1;
+    s.w0 = reinterpret_cast<const uint8_t*>(shared_w_gate);
+    s.w1 = reinterpret_cast<const uint8_t*>(shared_w_up);
+    s.s0 = shared_s_gate;
+    s.s1 = shared_s_up;
+    s.mtiles = I32(L.s_mtiles);
+    s.num_mtiles = I32(L.s_nmt);
+    s.offsets = I32(L.s_offsets);
+    s.max_mtiles = L.s_max_mtiles;
+    s.P = d->T;
+    s.I = (int)d->I_shared;
+    s.E = 1;
+    s.hq = reinterpret_cast<uint8_t*>(ws + L.s_hq);
+    s.hs_t = reinterpret_cast<float*>(ws + L.s_hs);
+    s.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.s_hq);
+    rc = tc1 ? moe_gemm1_tc(s, st) : moe_gemm1_simple(s, d->act_mode, st);
+    if (rc) return rc;
+    MoeGemmArgs s2 = s;
+    s2.aq = s.hq;
+    s2.as_t = s.hs_t;
+    s2.a16 = s.h16;
+    s2.w0 = reinterpret_cast<const uint8_t*>(shared_w_down);
+    s2.w1 = nullptr;
+    s2.s0 = shared_s_down;
+    s2.s1 = nullptr;
+    s2.out = reinterpret_cast<__nv_bfloat16*>(ws + L.s_y);
+    rc = tc2 ? moe_gemm2_tc(s2, st) : moe_gemm2_simple(s2, d->act_mode, st);
+    if (rc) return rc;
+    add = ws + L.s_y;
+  }
+  if (combined) {
+    rc = b200moe_combine(out, ws + L.y, topk_w, d->w_dtype, add, d->T, d->k, d->H, stream);
+    if (rc) return rc;
+  }
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
+
+extern "C" const char* b200moe_error_string(int code) {
+  switch (code) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_EINVAL: return "invalid argument (null pointer, non-positive size or unknown enum)";
+    case B200MOE_ESHAPE: return "unsupported size";
+    case B200MOE_EWORKSPACE: return "workspace too small or not 256-byte aligned";
+    case B200MOE_EALIGN: return "pointer not 16-byte aligned";
+    case B200MOE_EDRIVER: return "tensor-core path unavailable (no sm_100 device or no tensor-map driver entry point)";
+    default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "unknown error";
+  }
+}

@@ -1,0 +1,466 @@
+// Grouped FP8 (e4m3 x e4m3 -> fp32) expert GEMMs on the sm_100a tensor cores: tcgen05.mma with the
+// accumulator in tensor memory, operands staged in shared memory by TMA, block scales applied by the
+// epilogue warps ("promotion": every 128-deep K block is accumulated on its own in TMEM, read back,
+// multiplied by act_scale[row,kb] * weight_scale[nb,kb] and added to fp32 registers).
+//
+//   gemm1  h = SiLU(x Wg^T) * (x Wu^T)  per expert, then per-row 1x128 e4m3 requantisation
+//          (stands in for the gate/up part of my_ops/fusedMoE.pl:217-259)
+//   gemm2  y = h Wd                      per expert, rows scattered to their (token,slot) position
+//          (my_ops/fusedMoE.pl:264-269 + scatter_store :55-96)
+//
+// One persistent CTA per SM, 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and TMEM
+// owner, warps 2..9 = epilogue (TMEM lane quarter = warp%4, column half = (warp-2)/4).
+// A tile is 128 rows x 256 MMA columns: gemm1 -> 128 gate + 128 up columns of one 128-wide slice of I
+// (so SiLU*up and the 1x128 requantisation stay inside the CTA); gemm2 -> 256 columns of H.
+// Weights keep the reference layout [E,I,H]: for gemm1 the B operand is K-major, for gemm2 (K = I is the
+// slow axis) it is MN-major; both use the 128-byte swizzle that TMA writes.
+//
+// No multicast loads anywhere.  Every wait is bounded: on a time-out the CTA raises status bit 1, all roles
+// leave their loops, tensor memory is released and the kernel returns.
+#include <cuda.h>
+
+#include "internal.h"
+
+namespace {
+
+constexpr int TC_THREADS = 320;
+constexpr int TC_STAGES = 4;
+constexpr int TC_A_BYTES = 128 * 128;       // 128 rows x 128 B
+constexpr int TC_B_BYTES = 2 * 128 * 128;   // two 128 x 128 B boxes
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_TMEM_COLS = 512;           // two accumulator buffers of 256 fp32 columns
+constexpr uint32_t TC_SPIN_LIMIT = 4u << 20;  // polls (with back-off) before a wait gives up: ~1 s
+
+struct TcShared {
+  uint64_t full[TC_STAGES];
+  uint64_t empty[TC_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float amax[2][128];
+};
+constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
+
+struct TcArgs {
+  const float* as_t;
+  int64_t ld;
+  const void* s0;
+  const void* s1;
+  int scale_dtype;
+  const int32_t* mtiles;
+  const int32_t* num_mtiles;
+  const int32_t* offsets;
+  const int32_t* row_map;
+  int H, I, NT;
+  uint8_t* hq;
+  float* hs_t;
+  __nv_bfloat16* out;
+  int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when it gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 4096) __nanosleep(128);
+    if ((i & 255) == 255) {
+      if (*abort_flag) return false;
+      if (i > TC_SPIN_LIMIT) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread, completed before returning
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor of a 128-byte-swizzled operand tile (8-row x 128-byte atoms, 1024 B each).
+//   K-major : rows are M/N indices, 128 B of K per row; SBO = 1024 (next 8 rows); LBO unused (1)
+//   MN-major: rows are K indices, 128 B of M/N per row; SBO = 1024 (next 8 K rows); LBO = distance between
+//             128-wide M/N chunks
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) /*descriptor version of sm_100*/ |
+         (2ull << 61) /*128-byte swizzle*/;
+}
+// Instruction descriptor, kind::f8f6f4: D fp32, A/B e4m3, M = 128, N = 256
+__host__ __device__ constexpr uint32_t make_idesc(int b_mn_major) {
+  return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+template <bool GEMM2>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
+                   const __grid_constant__ CUtensorMap tmB1, const TcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)TC_STAGES * TC_STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), 1);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), 8);
+    }
+    sh->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sh->tmem_base)),
+                 "r"(TC_TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  const int num_mtiles = *a.num_mtiles;
+  const int total_tiles = num_mtiles * a.NT;
+  const int KB = (GEMM2 ? a.I : a.H) / kBlock;
+  const int nH = a.H / kBlock, nI = a.I / kBlock;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (one thread)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
+        const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % TC_STAGES;
+          const uint32_t ph = (it / TC_STAGES) & 1;
+          if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = smem_u32(&sh->full[s]);
+          const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+          mbar_arrive_expect_tx(full, TC_STAGE_BYTES);
+          tma_load_2d(sa, &tmA, kb * kBlock, row0, full);
+          if (!GEMM2) {
+            tma_load_2d(sb, &tmB0, kb * kBlock, e * a.I + nt * 128, full);
+            tma_load_2d(sb + 128 * 128, &tmB1, kb * kBlock, e * a.I + nt * 128, full);
+          } else {
+            tma_load_2d(sb, &tmB0, nt * 256, e * a.I + kb * kBlock, full);
+            tma_load_2d(sb + 128 * 128, &tmB0, nt * 256 + 128, e * a.I + kb * kBlock, full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (one thread)
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(GEMM2 ? 1 : 0);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % TC_STAGES;
+          const uint32_t ph = (it / TC_STAGES) & 1;
+          const int buf = it & 1;
+          const uint32_t bph = (it >> 1) & 1;
+          if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag) ||
+              !mbar_wait(smem_u32(&sh->tmem_empty[buf]), bph ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
+          const uint64_t adesc = make_smem_desc(sa, 16, 1024);
+          const uint64_t bdesc = GEMM2 ? make_smem_desc(sb, 128 * 128, 1024) : make_smem_desc(sb, 16, 1024);
+          const uint32_t d = tmem_base + buf * 256;
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            // K advances 32 elements: +32 B inside the swizzle atom (K-major) or +32 rows of 128 B (MN-major)
+            const uint64_t ad = adesc + (uint64_t)(ks * 2);
+            const uint64_t bd = bdesc + (uint64_t)(GEMM2 ? ks * 256 : ks * 2);
+            tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&sh->empty[s]));
+          tc_commit(smem_u32(&sh->tmem_full[buf]));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (8 warps)
+    const int q = warp & 3, hlf = (warp - 2) >> 2;
+    const int rit = q * 32 + lane;  // row inside the tile == TMEM lane
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
+      const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
+      const int row_end = a.offsets[e + 1];
+      const int grow = row0 + rit;
+      const bool valid = grow < row_end;
+      float acc[2][64];
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[j][i] = 0.f;
+      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]
+      const int64_t sbase = GEMM2 ? (int64_t)e * nI * nH + 2 * nt : ((int64_t)e * nI + nt) * nH;
+      const int64_t sstep = GEMM2 ? nH : 1;
+      const bool j1_in = GEMM2 ? (2 * nt + 1 < nH) : true;
+      float sa_n = valid ? a.as_t[grow] : 0.f;
+      float w0_n = moe_load_as_f32(a.s0, sbase, a.scale_dtype);
+      float w1_n = GEMM2 ? (j1_in ? moe_load_as_f32(a.s0, sbase + 1, a.scale_dtype) : 0.f)
+                         : moe_load_as_f32(a.s1, sbase, a.scale_dtype);
+      for (int kb = 0; kb < KB; ++kb, ++it) {
+        const float f0 = sa_n * w0_n, f1 = sa_n * w1_n;
+        if (kb + 1 < KB) {  // prefetch the next block's scales while this block's MMAs run
+          sa_n = valid ? a.as_t[(int64_t)(kb + 1) * a.ld + grow] : 0.f;
+          w0_n = moe_load_as_f32(a.s0, sbase + (kb + 1) * sstep, a.scale_dtype);
+          w1_n = GEMM2 ? (j1_in ? moe_load_as_f32(a.s0, sbase + (kb + 1) * sstep + 1, a.scale_dtype) : 0.f)
+                       : moe_load_as_f32(a.s1, sbase + (kb + 1) * sstep, a.scale_dtype);
+        }
+        const int buf = it & 1;
+        const uint32_t bph = (it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&sh->tmem_full[buf]), bph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hlf * 64;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            float v[32];
+            tc_ld32(tbase + j * 128 + c * 32, v);
+            if (j == 1 && c == 1) {  // all four chunks are in registers: hand the buffer back
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+            }
+            const float f = j == 0 ? f0 : f1;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[j][c * 32 + i] = fmaf(v[i], f, acc[j][c * 32 + i]);
+          }
+        }
+      }
+      if (!ok) break;
+      if (!GEMM2) {
+        // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over two warps
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float h = moe_silu(acc[0][i]) * acc[1][i];
+          acc[0][i] = h;
+          amax = fmaxf(amax, fabsf(h));
+        }
+        sh->amax[hlf][rit] = amax;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        amax = fmaxf(fmaxf(amax, sh->amax[hlf ^ 1][rit]), kAmaxFloor);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float inv = kFp8Max / amax;
+        if (valid) {
+          uint4* dst = reinterpret_cast<uint4*>(a.hq + (int64_t)grow * a.I + nt * 128 + hlf * 64);
+#pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const int i = v4 * 16 + w * 4;
+              ow[w] = moe_f32x4_to_e4m3x4(acc[0][i] * inv, acc[0][i + 1] * inv, acc[0][i + 2] * inv,
+                                          acc[0][i + 3] * inv);
+            }
+            dst[v4] = o;
+          }
+          if (hlf == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
+        }
+      } else if (valid) {
+        const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col = nt * 256 + j * 128 + hlf * 64;
+          if (col < a.H) {
+            uint4* dst = reinterpret_cast<uint4*>(a.out + dstrow * a.H + col);
+#pragma unroll
+            for (int v4 = 0; v4 < 8; ++v4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+              for (int w = 0; w < 4; ++w)
+                o2[w] = __floats2bfloat162_rn(acc[j][v4 * 8 + 2 * w], acc[j][v4 * 8 + 2 * w + 1]);
+              dst[v4] = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every role arrives here, also after a time-out ---------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (sh->abort_flag) {
+    if (threadIdx.x == 0 && a.status) atomicOr(a.status, B200MOE_STATUS_WAIT_TIMEOUT);
+    // give copies and MMAs that are still in flight time to land before shared/tensor memory is released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+  }
+}
+
+// ---- host side ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// row-major u8 matrix [rows, cols], box 128 x 128 bytes, 128-byte swizzle, zero fill outside
+bool make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols};
+  cuuint32_t box[2] = {128, 128};
+  cuuint32_t es[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, es,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int device_sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 1;
+  }();
+  return n;
+}
+
+template <bool GEMM2>
+int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
+  const int K = GEMM2 ? g.I : g.H;
+  CUtensorMap tmA, tmB0, tmB1;
+  if (!make_map_u8(&tmA, g.aq, (uint64_t)g.P, (uint64_t)K)) return B200MOE_EDRIVER;
+  if (!make_map_u8(&tmB0, g.w0, (uint64_t)g.E * g.I, (uint64_t)g.H)) return B200MOE_EDRIVER;
+  if (!make_map_u8(&tmB1, GEMM2 ? g.w0 : g.w1, (uint64_t)g.E * g.I, (uint64_t)g.H)) return B200MOE_EDRIVER;
+  TcArgs a{};
+  a.as_t = g.as_t;
+  a.ld = g.ld;
+  a.s0 = g.s0;
+  a.s1 = g.s1;
+  a.scale_dtype = g.scale_dtype;
+  a.mtiles = g.mtiles;
+  a.num_mtiles = g.num_mtiles;
+  a.offsets = g.offsets;
+  a.row_map = g.row_map;
+  a.H = g.H;
+  a.I = g.I;
+  a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
+  a.hq = g.hq;
+  a.hs_t = g.hs_t;
+  a.out = g.out;
+  a.status = g.status;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+    cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+    attr = true;
+  }
+  const long long max_tiles = (long long)g.max_mtiles * a.NT;
+  const int grid = (int)(max_tiles < device_sm_count() ? max_tiles : device_sm_count());
+  moe_gemm_tc_kernel<GEMM2><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
+  return moe_launch_status();
+}
+
+}  // namespace
+
+bool moe_tc_available() {
+  static bool ok = [] {
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    return major == 10 && get_encode_fn() != nullptr;
+  }();
+  return ok;
+}
+
+int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<false>(a, st); }
+int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<true>(a, st); }

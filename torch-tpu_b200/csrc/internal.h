@@ -1,0 +1,45 @@
+// Launchers shared between the translation units of libb200moe (not part of the C ABI).
+#pragma once
+#include "common.cuh"
+
+constexpr int kTileM = 128;  // rows of one m-tile of the grouped GEMMs
+
+// One grouped-GEMM problem: rows [0,P) sorted by expert, m-tiles built from expert_offsets.
+struct MoeGemmArgs {
+  // activations
+  const uint8_t* aq;        // W8A8: e4m3 [P,K]
+  const float* as_t;        // W8A8: scales [K/128, ld]
+  int64_t ld;               // leading dimension of transposed scale arrays
+  const __nv_bfloat16* a16; // W8A16: bf16 rows; gemm1: x [T,H] gathered through row_map/div; gemm2: h [P,I]
+  const int32_t* row_map;   // sorted_pair (flat t*k+j) or nullptr for identity
+  int div;                  // k (pair -> token)
+  // weights of this problem ([E,I,H] e4m3, scales [E,I/128,H/128])
+  const uint8_t* w0;        // gemm1: gate; gemm2: down
+  const uint8_t* w1;        // gemm1: up
+  const void* s0;
+  const void* s1;
+  int scale_dtype;
+  // tiling
+  const int32_t* mtiles;    // int2 {expert, row0} per m-tile
+  const int32_t* num_mtiles;
+  const int32_t* offsets;   // expert_offsets[E+1]
+  int max_mtiles;
+  int64_t P;
+  int H, I, E;
+  // outputs
+  uint8_t* hq;              // gemm1 W8A8: e4m3 [P,I]
+  float* hs_t;              // gemm1 W8A8: [I/128, ld]
+  __nv_bfloat16* h16;       // gemm1 W8A16: bf16 [P,I]
+  __nv_bfloat16* out;       // gemm2: bf16 rows of H, row index = row_map ? row_map[r] : r
+  int32_t* status;
+};
+
+int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, cudaStream_t st);
+// identity problem (one expert, rows 0..T): offsets = {0,T}
+int moe_fill_identity_offsets(int32_t* offsets, int64_t T, cudaStream_t st);
+
+int moe_gemm1_simple(const MoeGemmArgs& a, int act_mode, cudaStream_t st);
+int moe_gemm2_simple(const MoeGemmArgs& a, int act_mode, cudaStream_t st);
+int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st);
+int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st);
+bool moe_tc_available();

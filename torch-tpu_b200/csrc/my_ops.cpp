@@ -1,0 +1,309 @@
+// torch.ops.my_ops.* - the reference's custom-op surface for the fused-MoE path, same op names and the
+// same C++ signatures (hence the same inferred schemas) as torch_tpu/csrc/ops/my_ops/ops.hpp:279-306,
+// 610-676, 716-722, registered the way torch_tpu/csrc/ops/my_ops/myOps.cpp:29-80 does.  Each wrapper
+// validates its arguments (always, not only in debug builds as CHECK_TENSOR_IN_DEVICE does,
+// torch_tpu/csrc/core/TPUTorchUtils.h:70-92), takes the current CUDA stream where the reference takes the
+// current TPU stream (my_ops/fusedMoE.cpp:185) and calls the C ABI of libb200moe, checking its status the
+// way the reference checks tpudnnStatus_t (my_ops/fusedMoE.cpp:231).  There is no CPU fallback.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/library.h>
+#include <ATen/ATen.h>
+
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/b200moe.h"
+
+namespace at {
+namespace {
+
+void check_rc(int rc, const char* what) {
+  TORCH_CHECK(rc == B200MOE_OK, what, " failed: ", b200moe_error_string(rc), " (", rc, ")");
+}
+
+void check_cuda_contig(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+int scale_dtype_of(const Tensor& s) {
+  if (s.scalar_type() == kFloat) return B200MOE_F32;
+  if (s.scalar_type() == kBFloat16) return B200MOE_BF16;
+  TORCH_CHECK(false, "block scales must be float32 or bfloat16");
+}
+
+int score_dtype_of(const Tensor& s) {
+  if (s.scalar_type() == kFloat) return B200MOE_F32;
+  if (s.scalar_type() == kBFloat16) return B200MOE_BF16;
+  if (s.scalar_type() == kHalf) return B200MOE_F16;
+  TORCH_CHECK(false, "scores must be float32, bfloat16 or float16");
+}
+
+// MOE_ACT_MODE = w8a8 (default: e4m3 activations, FP8 tensor cores) | w8a16 (the reference's arithmetic)
+int act_mode_from_env() {
+  const char* v = std::getenv("MOE_ACT_MODE");
+  if (v && std::strcmp(v, "w8a16") == 0) return B200MOE_ACT_W8A16;
+  return B200MOE_ACT_W8A8;
+}
+
+// Grow-only workspace per (device, stream).  The reference's callers pass scratch tensors in; ours may pass
+// None, so the op layer keeps one buffer from torch's caching allocator.  The C ABI itself never allocates.
+Tensor workspace_for(const Device& dev, cudaStream_t st, size_t bytes) {
+  static std::mutex mu;
+  static std::unordered_map<uint64_t, Tensor> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  const uint64_t key = (uint64_t)reinterpret_cast<uintptr_t>(st) * 131 + (uint64_t)dev.index();
+  auto it = cache.find(key);
+  if (it == cache.end() || (size_t)it->second.numel() < bytes) {
+    Tensor t = at::empty({(int64_t)(bytes + bytes / 8 + 256)}, TensorOptions().dtype(kByte).device(dev));
+    cache[key] = t;
+    return t;
+  }
+  return it->second;
+}
+
+Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, const Tensor& up_w,
+                   const Tensor& down_w, const Tensor& gate_s, const Tensor& up_s, const Tensor& down_s,
+                   const Tensor& select_experts, const Tensor& routing_weights, int64_t blocksize,
+                   int64_t num_experts, int64_t top_k, int act_mode) {
+  check_cuda_contig(output, "output");
+  check_cuda_contig(input, "input");
+  check_cuda_contig(gate_w, "gate_weights");
+  check_cuda_contig(up_w, "up_weights");
+  check_cuda_contig(down_w, "down_weights");
+  check_cuda_contig(gate_s, "gate_scales");
+  check_cuda_contig(up_s, "up_scales");
+  check_cuda_contig(down_s, "down_scales");
+  check_cuda_contig(select_experts, "select_experts");
+  check_cuda_contig(routing_weights, "routing_weights");
+  TORCH_CHECK(select_experts.scalar_type() == kInt, "select_experts must be int32 dtype");
+  TORCH_CHECK(blocksize == 128, "blocksize must be 128");
+  TORCH_CHECK(input.dim() == 2 && input.scalar_type() == kBFloat16, "input must be bf16 [T,H]");
+  TORCH_CHECK(output.scalar_type() == kBFloat16, "output must be bf16");
+  TORCH_CHECK(gate_w.scalar_type() == kFloat8_e4m3fn && up_w.scalar_type() == kFloat8_e4m3fn &&
+                  down_w.scalar_type() == kFloat8_e4m3fn,
+              "expert weights must be float8_e4m3fn");
+  const int64_t T = input.size(0), H = input.size(1);
+  TORCH_CHECK(gate_w.dim() == 3 && gate_w.size(0) == num_experts && gate_w.size(2) == H,
+              "gate_weights must be [E,I,H]");
+  const int64_t I = gate_w.size(1);
+  TORCH_CHECK(up_w.sizes() == gate_w.sizes() && down_w.sizes() == gate_w.sizes(),
+              "up/down weights must be [E,I,H] (down = W_down^T, contiguous)");
+  const int64_t nI = (I + 127) / 128, nH = (H + 127) / 128;
+  for (const Tensor* s : {&gate_s, &up_s, &down_s})
+    TORCH_CHECK(s->dim() == 3 && s->size(0) == num_experts && s->size(1) == nI && s->size(2) == nH,
+                "block scales must be [E, I/128, H/128]");
+  TORCH_CHECK(gate_s.scalar_type() == up_s.scalar_type() && gate_s.scalar_type() == down_s.scalar_type(),
+              "the three scale tensors must share a dtype");
+  TORCH_CHECK(select_experts.dim() == 2 && select_experts.size(0) == T && select_experts.size(1) == top_k,
+              "select_experts must be [T,k]");
+  TORCH_CHECK(routing_weights.numel() == T * top_k, "routing_weights must be [T,k]");
+
+  b200moe_experts_desc d{};
+  d.T = T;
+  d.H = H;
+  d.I = I;
+  d.E = num_experts;
+  d.k = top_k;
+  d.I_shared = 0;
+  if (output.dim() == 3) {
+    TORCH_CHECK(output.size(0) == T && output.size(1) == top_k && output.size(2) == H, "output must be [T,k,H]");
+    d.out_mode = B200MOE_OUT_PER_SLOT;
+  } else {
+    TORCH_CHECK(output.dim() == 2 && output.size(0) == T && output.size(1) == H, "output must be [T,k,H] or [T,H]");
+    d.out_mode = B200MOE_OUT_COMBINED;
+  }
+  d.act_mode = act_mode;
+  d.impl = B200MOE_IMPL_AUTO;
+  d.scale_dtype = scale_dtype_of(gate_s);
+  if (routing_weights.scalar_type() == kFloat) d.w_dtype = B200MOE_F32;
+  else if (routing_weights.scalar_type() == kBFloat16) d.w_dtype = B200MOE_BF16;
+  else TORCH_CHECK(false, "routing_weights must be float32 or bfloat16");
+
+  c10::cuda::CUDAGuard guard(input.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  const size_t need = b200moe_experts_workspace_bytes(&d);
+  TORCH_CHECK(need > 0 || T == 0, "fused_moe_fused_experts: unsupported sizes (H and I must be multiples of 128)");
+  Tensor ws = workspace_for(input.device(), st, need);
+  void* wsp = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 255) & ~uintptr_t(255));
+  const size_t ws_bytes = (size_t)ws.numel() - (reinterpret_cast<char*>(wsp) - reinterpret_cast<char*>(ws.data_ptr()));
+  int rc = b200moe_experts(output.data_ptr(), input.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(),
+                           down_w.data_ptr(), gate_s.data_ptr(), up_s.data_ptr(), down_s.data_ptr(),
+                           select_experts.data_ptr<int32_t>(), routing_weights.data_ptr(), nullptr, nullptr,
+                           nullptr, nullptr, nullptr, nullptr, &d, wsp, ws_bytes, nullptr, st);
+  check_rc(rc, "b200moe_experts");
+  return output;
+}
+
+void reject_unused(const c10::optional<Tensor>& output_sample, const c10::optional<Tensor>& input_sample,
+                   const c10::optional<Tensor>& num_select_experts, const c10::optional<Tensor>& silu,
+                   const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0, bool save_mid_res) {
+  // None/False in every reference call (python/regression/test_llm/test_moe.py:105-107,129,140)
+  TORCH_CHECK(!output_sample.has_value() && !input_sample.has_value(),
+              "output_sample / input_sample are not supported (pass None)");
+  if (num_select_experts.has_value())
+    TORCH_CHECK(num_select_experts.value().scalar_type() == kLong, "num_select_experts must be int64 dtype");
+  TORCH_CHECK(!silu.has_value() && !sigmoid.has_value() && !m0.has_value() && !save_mid_res,
+              "saving intermediate results (silu/sigmoid/m0/save_mid_res) is not supported");
+}
+
+}  // namespace
+
+Tensor fused_moe_fused_experts(
+    Tensor& output, Tensor& input, const c10::optional<Tensor>& output_sample,
+    const c10::optional<Tensor>& input_sample, Tensor& gate_weights, Tensor& up_weights, Tensor& down_weights,
+    const c10::optional<Tensor>& gate_scales, const c10::optional<Tensor>& up_scales,
+    const c10::optional<Tensor>& down_scales, Tensor& select_experts, Tensor& routing_weights,
+    const c10::optional<Tensor>& num_select_experts, const c10::optional<Tensor>& select_experts_middle,
+    const c10::optional<Tensor>& routing_weights_middle, int64_t blocksize, int64_t num_experts,
+    int64_t num_experts_per_tok, bool use_grouped_topk, int64_t num_expert_group, int64_t topk_group,
+    const c10::optional<Tensor>& silu, const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0,
+    bool save_mid_res) {
+  reject_unused(output_sample, input_sample, num_select_experts, silu, sigmoid, m0, save_mid_res);
+  TORCH_CHECK(gate_scales.has_value() && up_scales.has_value() && down_scales.has_value(),
+              "fused_moe_fused_experts: FP8 weights need their block scales (bf16-weight experts are out of scope)");
+  (void)select_experts_middle;  // caller scratch of the reference kernels; not needed here
+  (void)routing_weights_middle;
+  (void)use_grouped_topk;       // routing is already done: select_experts is an input
+  (void)num_expert_group;
+  (void)topk_group;
+  return run_experts(output, input, gate_weights, up_weights, down_weights, gate_scales.value(), up_scales.value(),
+                     down_scales.value(), select_experts, routing_weights, blocksize, num_experts,
+                     num_experts_per_tok, act_mode_from_env());
+}
+
+Tensor fused_moe_fused_experts_v2(
+    Tensor& output, Tensor& input, const c10::optional<Tensor>& output_sample,
+    const c10::optional<Tensor>& input_sample, Tensor& gate_weights, Tensor& up_weights, Tensor& down_weights,
+    const c10::optional<Tensor>& gate_scales, const c10::optional<Tensor>& up_scales,
+    const c10::optional<Tensor>& down_scales, Tensor& select_experts, Tensor& routing_weights,
+    const c10::optional<Tensor>& num_select_experts, const c10::optional<Tensor>& select_experts_middle,
+    const c10::optional<Tensor>& routing_weights_middle, const c10::optional<Tensor>& gather_buffer,
+    const c10::optional<Tensor>& scatter_buffer, int64_t blocksize, int64_t num_experts,
+    int64_t num_experts_per_tok, bool use_grouped_topk, int64_t num_expert_group, int64_t topk_group,
+    const c10::optional<Tensor>& silu, const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0,
+    bool save_mid_res) {
+  (void)gather_buffer;
+  (void)scatter_buffer;
+  return fused_moe_fused_experts(output, input, output_sample, input_sample, gate_weights, up_weights,
+                                 down_weights, gate_scales, up_scales, down_scales, select_experts,
+                                 routing_weights, num_select_experts, select_experts_middle,
+                                 routing_weights_middle, blocksize, num_experts, num_experts_per_tok,
+                                 use_grouped_topk, num_expert_group, topk_group, silu, sigmoid, m0, save_mid_res);
+}
+
+// Router matmul + softmax + top-k with caller-provided scratch (my_ops/fusedMoE.cpp:82-115).  The reference
+// has no test and no CPU twin of this op and its device code is closed, so the mapping of the ten tensors is
+// inferred from their names: left [T,H] and right [E,H] fp32 with bf16 copies, matmul_res / softmax_res [T,E]
+// fp32, max [T] fp32, topk_weights_res [T,k] fp32 (+ bf16 copy), topk_experts_res [T,k] int32.  Here:
+// logits = left_bf16 . right_bf16^T, softmax, top-k, weights renormalised to sum 1.
+Tensor fused_moe_grouped_topk(Tensor& topk_experts_res, Tensor& topk_weights_res_bf16, Tensor& left_bf16,
+                              Tensor& right_bf16, Tensor& topk_weights_res, Tensor& left, Tensor& right,
+                              Tensor& max, Tensor& matmul_res, Tensor& softmax_res) {
+  check_cuda_contig(topk_experts_res, "topk_experts_res");
+  check_cuda_contig(topk_weights_res_bf16, "topk_weights_res_bf16");
+  check_cuda_contig(left_bf16, "left_bf16");
+  check_cuda_contig(right_bf16, "right_bf16");
+  check_cuda_contig(topk_weights_res, "topk_weights_res");
+  check_cuda_contig(matmul_res, "matmul_res");
+  TORCH_CHECK(topk_experts_res.scalar_type() == kInt, "topk_experts_res must be int32");
+  TORCH_CHECK(left_bf16.scalar_type() == kBFloat16 && right_bf16.scalar_type() == kBFloat16 &&
+                  topk_weights_res_bf16.scalar_type() == kBFloat16,
+              "*_bf16 tensors must be bfloat16");
+  TORCH_CHECK(topk_weights_res.scalar_type() == kFloat && matmul_res.scalar_type() == kFloat,
+              "topk_weights_res and matmul_res must be float32");
+  TORCH_CHECK(left_bf16.dim() == 2 && right_bf16.dim() == 2 && left_bf16.size(1) == right_bf16.size(1),
+              "left_bf16 [T,H], right_bf16 [E,H]");
+  const int64_t T = left_bf16.size(0), H = left_bf16.size(1), E = right_bf16.size(0);
+  TORCH_CHECK(topk_experts_res.dim() == 2 && topk_experts_res.size(0) == T, "topk_experts_res must be [T,k]");
+  const int64_t k = topk_experts_res.size(1);
+  TORCH_CHECK(matmul_res.numel() == T * E && topk_weights_res.numel() == T * k &&
+                  topk_weights_res_bf16.numel() == T * k,
+              "scratch/result shapes do not match [T,E] / [T,k]");
+  (void)left;
+  (void)right;
+  (void)max;
+  (void)softmax_res;
+  c10::cuda::CUDAGuard guard(left_bf16.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  check_rc(b200moe_router_logits(matmul_res.data_ptr<float>(), left_bf16.data_ptr(), right_bf16.data_ptr(), T, H, E, st),
+           "b200moe_router_logits");
+  check_rc(b200moe_route(topk_experts_res.data_ptr<int32_t>(), topk_weights_res.data_ptr<float>(),
+                         topk_weights_res_bf16.data_ptr(), matmul_res.data_ptr<float>(), nullptr, T, E, k,
+                         B200MOE_SCORE_SOFTMAX, 1, 1, 1, 1.0f, st),
+           "b200moe_route");
+  return topk_experts_res;
+}
+
+// my_ops/NoauxTcTopk.cpp:9-67 - same checks, same order of arguments
+Tensor noaux_tc_topk(Tensor& values, Tensor& indices, const Tensor& scores, int64_t n_groups,
+                     int64_t topk_groups, int64_t top_k) {
+  check_cuda_contig(values, "values");
+  check_cuda_contig(indices, "indices");
+  check_cuda_contig(scores, "scores");
+  TORCH_CHECK(values.dtype() == scores.dtype(), "values and scores must have the same dtype");
+  TORCH_CHECK(indices.dtype() == kInt, "indices must be int32");
+  TORCH_CHECK(scores.dim() == 2, "scores must be 2D tensor");
+  const int64_t batch_size = scores.size(0), total_size = scores.size(1);
+  TORCH_CHECK(values.dim() == 2 && values.size(0) == batch_size && values.size(1) == top_k,
+              "values shape must be [batch_size, top_k]");
+  TORCH_CHECK(indices.dim() == 2 && indices.size(0) == batch_size && indices.size(1) == top_k,
+              "indices shape must be [batch_size, top_k]");
+  TORCH_CHECK(n_groups > 0 && total_size % n_groups == 0, "total_size must be divisible by n_groups");
+  TORCH_CHECK(topk_groups <= n_groups, "topk_groups must be <= n_groups");
+  TORCH_CHECK(top_k > 0, "top_k must be positive");
+  c10::cuda::CUDAGuard guard(scores.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  check_rc(b200moe_noaux_tc_topk(values.data_ptr(), indices.data_ptr<int32_t>(), scores.data_ptr(),
+                                 score_dtype_of(scores), batch_size, total_size, n_groups, topk_groups, top_k, st),
+           "b200moe_noaux_tc_topk");
+  return values;
+}
+
+namespace {
+// Dense FP8 gated MLP = one expert applied to every row (the shared-expert op).  Weights [I,H] x3 with the
+// down projection passed transposed (python/regression/test_llm/test_mlp_w8a16_dq.py:102-105).
+Tensor dense_mlp(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& down_weight, Tensor& gate_scale,
+                 Tensor& up_scale, Tensor& down_scale, Tensor& output, int64_t blocksize, int act_mode) {
+  TORCH_CHECK(input.dim() == 2 && gate_weight.dim() == 2, "input [T,H], weights [I,H]");
+  TORCH_CHECK(output.dim() == 2 && output.sizes() == input.sizes(), "output must be [T,H]");
+  const int64_t T = input.size(0);
+  Tensor ids = at::zeros({T, 1}, input.options().dtype(kInt));
+  Tensor w = at::ones({T, 1}, input.options().dtype(kFloat));
+  Tensor out3 = output.view({T, 1, input.size(1)});
+  Tensor gw = gate_weight.unsqueeze(0), uw = up_weight.unsqueeze(0), dw = down_weight.unsqueeze(0);
+  Tensor gs = gate_scale.unsqueeze(0), us = up_scale.unsqueeze(0), ds = down_scale.unsqueeze(0);
+  run_experts(out3, input, gw, uw, dw, gs, us, ds, ids, w, blocksize, 1, 1, act_mode);
+  return output;
+}
+}  // namespace
+
+// my_ops/MlpW8A16Dq.cpp:189-243 (reference arithmetic: bf16 activations)
+Tensor mlp_w8a16_dq_forward(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& down_weight,
+                            Tensor& gate_scale, Tensor& up_scale, Tensor& down_scale, Tensor& output,
+                            int64_t blocksize) {
+  return dense_mlp(input, gate_weight, up_weight, down_weight, gate_scale, up_scale, down_scale, output, blocksize,
+                   B200MOE_ACT_W8A16);
+}
+
+// my_ops/MlpW8A8Quant.cpp:12-50 (activations quantised: FP8 tensor cores)
+Tensor mlp_w8a8_quant_forward(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& down_weight,
+                              Tensor& gate_scale, Tensor& up_scale, Tensor& down_scale, Tensor& output,
+                              int64_t blocksize) {
+  return dense_mlp(input, gate_weight, up_weight, down_weight, gate_scale, up_scale, down_scale, output, blocksize,
+                   B200MOE_ACT_W8A8);
+}
+
+TORCH_LIBRARY(my_ops, m) {
+  m.def("fused_moe_grouped_topk", fused_moe_grouped_topk);
+  m.def("fused_moe_fused_experts", fused_moe_fused_experts);
+  m.def("fused_moe_fused_experts_v2", fused_moe_fused_experts_v2);
+  m.def("noaux_tc_topk", noaux_tc_topk);
+  m.def("mlp_w8a16_dq_forward", mlp_w8a16_dq_forward);
+  m.def("mlp_w8a8_quant_forward", mlp_w8a8_quant_forward);
+}
+
+}  // namespace at

@@ -1,0 +1,241 @@
+// Token permutation: a STABLE counting sort of the T*k (token,slot) pairs by expert id, the tile list
+// that the grouped GEMMs walk, and the row gather + 1x128 e4m3 activation quantisation.
+//
+// The sort reproduces the reference device kernel's per-expert `nonzero` (my_ops/fusedMoE.pl:737-755):
+// inside one expert the flat pair ids t*k+j ascend.  It is deterministic (no atomics decide order):
+//   hist    : chunk c (1024 pairs) counts its pairs per expert            -> chunk_cnt[c][e]
+//   scan    : per expert a running sum over chunks, then a scan over experts -> chunk_base, offsets
+//   scatter : position = offsets[e] + chunk_base[c][e] + (pairs of e in earlier warps of the chunk)
+//             + (pairs of e in lower lanes of the warp)
+// For P <= 1024 all three steps run in one single-CTA kernel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kChunk = 1024;  // pairs per CTA (32 warps)
+constexpr int kMaxE = 1024;
+
+// Per-warp histogram of this chunk in shared memory: wh[w*E + e].  Returns the pair's expert (or -1)
+// and its rank among equal experts in lower lanes of its warp.
+__device__ __forceinline__ int chunk_hist(const int32_t* __restrict__ ids, int64_t P, int E, int64_t p,
+                                          int* wh, int& rank_in_warp, int32_t* status) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) wh[i] = 0;
+  __syncthreads();
+  int e = -1;
+  if (p < P) {
+    e = ids[p];
+    if (e < 0 || e >= E) {
+      e = -1;
+      if (status) atomicOr(status, B200MOE_STATUS_BAD_EXPERT);
+    }
+  }
+  unsigned peers = __match_any_sync(0xffffffffu, e);
+  rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) wh[warp * E + e] = __popc(peers);
+  __syncthreads();
+  return e;
+}
+
+__global__ void __launch_bounds__(kChunk)
+permute_hist_kernel(const int32_t* __restrict__ ids, int64_t P, int E, int32_t* __restrict__ chunk_cnt,
+                    int32_t* status) {
+  extern __shared__ int wh[];
+  int rank;
+  chunk_hist(ids, P, E, (int64_t)blockIdx.x * kChunk + threadIdx.x, wh, rank, status);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int s = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) s += wh[w * E + e];
+    chunk_cnt[(int64_t)blockIdx.x * E + e] = s;
+  }
+}
+
+// exclusive scan of cnt[0..E) by one CTA of 1024 threads (E <= 1024); result in offs[0..E], smem tmp[1024]
+__device__ __forceinline__ void block_exclusive_scan(int my, int E, int32_t* __restrict__ offs, int* tmp) {
+  const int t = threadIdx.x;
+  tmp[t] = t < E ? my : 0;
+  __syncthreads();
+  for (int d = 1; d < kChunk; d <<= 1) {
+    int v = t >= d ? tmp[t - d] : 0;
+    __syncthreads();
+    tmp[t] += v;
+    __syncthreads();
+  }
+  if (t < E) offs[t + 1] = tmp[t];
+  if (t == 0) offs[0] = 0;
+}
+
+__global__ void __launch_bounds__(kChunk)
+permute_scan_kernel(int32_t* __restrict__ chunk_cnt, int nchunks, int E, int32_t* __restrict__ offsets) {
+  __shared__ int tmp[kChunk];
+  int total = 0;
+  if ((int)threadIdx.x < E) {
+    for (int c = 0; c < nchunks; ++c) {
+      int v = chunk_cnt[(int64_t)c * E + threadIdx.x];
+      chunk_cnt[(int64_t)c * E + threadIdx.x] = total;  // becomes chunk_base
+      total += v;
+    }
+  }
+  block_exclusive_scan(total, E, offsets, tmp);
+}
+
+__global__ void __launch_bounds__(kChunk)
+permute_scatter_kernel(const int32_t* __restrict__ ids, int64_t P, int E,
+                       const int32_t* __restrict__ chunk_base, const int32_t* __restrict__ offsets,
+                       int32_t* __restrict__ sorted_pair) {
+  extern __shared__ int wh[];
+  int rank;
+  const int64_t p = (int64_t)blockIdx.x * kChunk + threadIdx.x;
+  int e = chunk_hist(ids, P, E, p, wh, rank, nullptr);
+  for (int x = threadIdx.x; x < E; x += blockDim.x) {  // warp histogram -> exclusive prefix over warps
+    int s = 0;
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) {
+      int v = wh[w * E + x];
+      wh[w * E + x] = s;
+      s += v;
+    }
+  }
+  __syncthreads();
+  if (e >= 0) {
+    int pos = offsets[e] + chunk_base[(int64_t)blockIdx.x * E + e] + wh[(threadIdx.x >> 5) * E + e] + rank;
+    sorted_pair[pos] = (int32_t)p;
+  }
+}
+
+// P <= 1024: histogram, scan and scatter in one CTA
+__global__ void __launch_bounds__(kChunk)
+permute_small_kernel(const int32_t* __restrict__ ids, int64_t P, int E, int32_t* __restrict__ offsets,
+                     int32_t* __restrict__ sorted_pair, int32_t* status) {
+  extern __shared__ int wh[];
+  __shared__ int tmp[kChunk];
+  __shared__ int soffs[kMaxE + 1];
+  int rank;
+  int e = chunk_hist(ids, P, E, threadIdx.x, wh, rank, status);
+  int total = 0;
+  if ((int)threadIdx.x < E) {
+#pragma unroll 8
+    for (int w = 0; w < 32; ++w) {
+      int v = wh[w * E + threadIdx.x];
+      wh[w * E + threadIdx.x] = total;
+      total += v;
+    }
+  }
+  block_exclusive_scan(total, E, soffs, tmp);
+  __syncthreads();
+  for (int i = threadIdx.x; i <= E; i += blockDim.x) offsets[i] = soffs[i];
+  if (e >= 0) sorted_pair[soffs[e] + wh[(threadIdx.x >> 5) * E + e] + rank] = (int32_t)threadIdx.x;
+}
+
+__global__ void gather_scatter_index_kernel(int32_t* __restrict__ gather_index,
+                                            int32_t* __restrict__ scatter_index,
+                                            int32_t* __restrict__ num_per_expert,
+                                            const int32_t* __restrict__ sorted_pair,
+                                            const int32_t* __restrict__ offsets, int64_t T, int k) {
+  const int e = blockIdx.x;
+  const int b = offsets[e], n = offsets[e + 1] - b;
+  if (threadIdx.x == 0) num_per_expert[e] = n;
+  for (int i = threadIdx.x; i < n && i < T; i += blockDim.x) {
+    int pr = sorted_pair[b + i];
+    scatter_index[(int64_t)e * T + i] = pr;
+    gather_index[(int64_t)e * T + i] = pr / k;
+  }
+}
+
+// ---- row gather + 1x128 e4m3 quantisation -------------------------------------------------------
+// One warp per output row; a lane owns 8 consecutive bf16 (one 16-byte load), 16 lanes own one
+// 128-column group, so a warp step covers two groups.
+__global__ void __launch_bounds__(256)
+quant_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ s_t, int64_t ld,
+                  const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ row_map, int div,
+                  int64_t rows, int H) {
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int64_t src = row_map ? (int64_t)(row_map[r] / div) : r;
+  const __nv_bfloat16* xr = x + src * H;
+  for (int c0 = 0; c0 < H; c0 += 256) {
+    const int c = c0 + lane * 8;
+    float v[8];
+    float amax = 0.f;
+    if (c < H) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(b2[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (c < H) {
+      amax = fmaxf(amax, kAmaxFloor);
+      const float inv = kFp8Max / amax;
+      uint2 out;
+      out.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+      out.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+      *reinterpret_cast<uint2*>(q + r * H + c) = out;
+      if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld + r] = amax / kFp8Max;
+    }
+  }
+}
+
+}  // namespace
+
+extern "C" size_t b200moe_permute_scratch_ints(int64_t P, int64_t E) {
+  if (P <= kChunk) return 1;
+  return (size_t)((P + kChunk - 1) / kChunk) * (size_t)E;
+}
+
+extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
+                               int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(sorted_pair && expert_offsets && ids && T >= 0 && k > 0 && E > 0);
+  const int64_t P = T * k;
+  MOE_CHECK_SHAPE(E <= kMaxE && P < (1 << 24));
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t smem = (size_t)32 * E * sizeof(int);
+  static bool attr_done = false;  // raising the dynamic shared-memory cap is per-function, idempotent
+  if (!attr_done) {
+    cudaFuncSetAttribute(permute_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
+    cudaFuncSetAttribute(permute_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
+    cudaFuncSetAttribute(permute_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
+    attr_done = true;
+  }
+  if (P <= kChunk) {
+    permute_small_kernel<<<1, kChunk, smem, st>>>(ids, P, (int)E, expert_offsets, sorted_pair, status);
+    return moe_launch_status();
+  }
+  MOE_CHECK_ARG(scratch);
+  const int nchunks = (int)((P + kChunk - 1) / kChunk);
+  permute_hist_kernel<<<nchunks, kChunk, smem, st>>>(ids, P, (int)E, scratch, status);
+  permute_scan_kernel<<<1, kChunk, 0, st>>>(scratch, nchunks, (int)E, expert_offsets);
+  permute_scatter_kernel<<<nchunks, kChunk, smem, st>>>(ids, P, (int)E, scratch, expert_offsets, sorted_pair);
+  return moe_launch_status();
+}
+
+extern "C" int b200moe_gather_scatter_index(int32_t* gather_index, int32_t* scatter_index,
+                                            int32_t* num_per_expert, const int32_t* sorted_pair,
+                                            const int32_t* expert_offsets, int64_t T, int64_t k, int64_t E,
+                                            void* stream) {
+  MOE_CHECK_ARG(gather_index && scatter_index && num_per_expert && sorted_pair && expert_offsets);
+  MOE_CHECK_ARG(T >= 0 && k > 0 && E > 0);
+  if (T == 0) return B200MOE_OK;
+  gather_scatter_index_kernel<<<(unsigned)E, 256, 0, (cudaStream_t)stream>>>(
+      gather_index, scatter_index, num_per_expert, sorted_pair, expert_offsets, T, (int)k);
+  return moe_launch_status();
+}
+
+extern "C" int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void* x, const int32_t* row_map,
+                                  int64_t div, int64_t rows, int64_t H, void* stream) {
+  MOE_CHECK_ARG(q && s_t && x && rows >= 0 && H > 0 && div > 0 && ld >= rows);
+  MOE_CHECK_SHAPE(H % kBlock == 0);
+  if (!moe_aligned16(x) || !moe_aligned16(q)) return B200MOE_EALIGN;
+  if (rows == 0) return B200MOE_OK;
+  quant_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      q, s_t, ld, reinterpret_cast<const __nv_bfloat16*>(x), row_map, (int)div, rows, (int)H);
+  return moe_launch_status();
+}

@@ -1,0 +1,83 @@
+"""FusedMoE: the caller-side wrapper that the reference leaves to model code - router matmul, routing chain
+(python/regression/test_llm/test_torch_ops.py:439-455), the fused experts op
+(python/regression/test_llm/test_moe.py:131-140) and the weighted combine (test_bmm.py:118-134) - as one call
+that allocates nothing after construction (all buffers are sized for ``max_tokens`` up front)."""
+from dataclasses import dataclass
+from typing import Optional, Tuple
+
+import torch
+
+from . import lib as L
+from . import ops
+
+
+@dataclass
+class MoEConfig:
+    hidden: int
+    intermediate: int
+    num_experts: int
+    top_k: int
+    score_func: str = "softmax"      # "softmax" | "sigmoid"
+    n_groups: int = 1                # group-limited routing (DeepSeek-V3: 8)
+    topk_groups: int = 1             # groups kept (DeepSeek-V3: 4)
+    renorm: bool = True              # weights / sum(weights)
+    routed_scale: float = 1.0        # DeepSeek-V3: 2.5
+    shared_intermediate: int = 0     # 0 = no shared expert
+
+
+class FusedMoE:
+    """One MoE layer on one GPU.  Weights are in the op layout: gate/up/down ``[E,I,H]`` float8_e4m3fn (down =
+    W_down^T contiguous), scales ``[E,I/128,H/128]`` fp32 or bf16, router ``[E,H]`` bf16, optional selection bias
+    ``[E]`` fp32, optional shared expert ``(wg,wu,wd,sg,su,sd)`` with a leading dim of 1."""
+
+    def __init__(self, cfg: MoEConfig, router_w, wg, wu, wd, sg, su, sd, bias=None, shared: Optional[Tuple] = None,
+                 max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO):
+        self.cfg = cfg
+        self.router_w, self.bias = router_w, bias
+        self.w = (wg, wu, wd, sg, su, sd)
+        self.shared = shared
+        self.act_mode, self.impl = act_mode, impl
+        dev = wg.device
+        self.device = dev
+        self.max_tokens = max_tokens
+        E, k, H = cfg.num_experts, cfg.top_k, cfg.hidden
+        self.logits = torch.empty(max_tokens, E, dtype=torch.float32, device=dev)
+        self.ids = torch.empty(max_tokens, k, dtype=torch.int32, device=dev)
+        self.topk_w = torch.empty(max_tokens, k, dtype=torch.float32, device=dev)
+        self.out = torch.empty(max_tokens, H, dtype=torch.bfloat16, device=dev)
+        self.x_dev = torch.empty(max_tokens, H, dtype=torch.bfloat16, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        d = ops.make_desc(max_tokens, H, cfg.intermediate, E, k, I_shared=cfg.shared_intermediate,
+                          out_mode=L.OUT_COMBINED, act_mode=act_mode, impl=impl, scale_dtype=sg.dtype)
+        self.workspace = torch.empty(ops.experts_workspace_bytes(d) + 256, dtype=torch.uint8, device=dev)
+
+    def route(self, x):
+        T = x.shape[0]
+        c = self.cfg
+        logits = ops.router_logits(x, self.router_w, out=self.logits[:T])
+        return ops.route(logits, c.top_k, c.score_func, self.bias, c.n_groups, c.topk_groups, c.renorm,
+                         c.routed_scale, ids=self.ids[:T], w=self.topk_w[:T])
+
+    def forward(self, x, out=None):
+        """x bf16 [T,H] on the device -> bf16 [T,H] (a view of an internal buffer unless ``out`` is given)."""
+        T = x.shape[0]
+        if T > self.max_tokens:
+            raise ValueError(f"{T} tokens > max_tokens={self.max_tokens}")
+        ids, w = self.route(x)
+        if out is None:
+            out = self.out[:T]
+        wg, wu, wd, sg, su, sd = self.w
+        return ops.experts(out, x, wg, wu, wd, sg, su, sd, ids, w, shared=self.shared, act_mode=self.act_mode,
+                           impl=self.impl, workspace=self.workspace, status=self.status)
+
+    __call__ = forward
+
+    def forward_host(self, x_host, out_host):
+        """End-to-end call with HOST buffers (pinned for asynchronous copies): H2D of x, the layer, D2H of the
+        result, all on the current stream.  Returns out_host (valid after a stream synchronise)."""
+        T = x_host.shape[0]
+        xd = self.x_dev[:T]
+        xd.copy_(x_host, non_blocking=True)
+        y = self.forward(xd)
+        out_host.copy_(y, non_blocking=True)
+        return out_host

@@ -1,0 +1,167 @@
+"""Functional wrappers over the C ABI taking torch CUDA tensors (device memory and streams are torch's;
+the arithmetic is all in libb200moe).  Every function enqueues on torch's current stream and returns
+without synchronising.  Inputs must be contiguous CUDA tensors; nothing here falls back to PyTorch math."""
+import ctypes
+
+import torch
+
+from . import lib as L
+
+_DT = {torch.float32: L.F32, torch.bfloat16: L.BF16, torch.float16: L.F16}
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _chk(t, name, dtype=None):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda and t.is_contiguous()):
+        raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def noaux_tc_topk(scores, n_groups, topk_groups, top_k):
+    """Grouped top-k (reference op my_ops.noaux_tc_topk, my_ops/NoauxTcTopk.cpp:9-67).
+    Returns (values [B,k] in scores' dtype, indices [B,k] int32)."""
+    _chk(scores, "scores")
+    B, E = scores.shape
+    values = torch.empty(B, top_k, dtype=scores.dtype, device=scores.device)
+    indices = torch.empty(B, top_k, dtype=torch.int32, device=scores.device)
+    L.check(L.lib().b200moe_noaux_tc_topk(_ptr(values), _ptr(indices), _ptr(scores), _DT[scores.dtype], B, E,
+                                          n_groups, topk_groups, top_k, _stream()), "b200moe_noaux_tc_topk")
+    return values, indices
+
+
+def topk(x, k):
+    """Descending top-k along the last dim with int32 indices (aten::topk on the reference device,
+    native_ops/Topk.cpp:90-150)."""
+    _chk(x, "x")
+    B, n = x.shape
+    values = torch.empty(B, k, dtype=x.dtype, device=x.device)
+    indices = torch.empty(B, k, dtype=torch.int32, device=x.device)
+    L.check(L.lib().b200moe_topk(_ptr(values), _ptr(indices), _ptr(x), _DT[x.dtype], B, n, k, _stream()),
+            "b200moe_topk")
+    return values, indices
+
+
+def router_logits(x, wr, out=None):
+    _chk(x, "x", torch.bfloat16)
+    _chk(wr, "wr", torch.bfloat16)
+    T, H = x.shape
+    E = wr.shape[0]
+    if out is None:
+        out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    L.check(L.lib().b200moe_router_logits(_ptr(out), _ptr(x), _ptr(wr), T, H, E, _stream()), "b200moe_router_logits")
+    return out
+
+
+def route(logits, k, score_func="softmax", bias=None, n_groups=1, topk_groups=1, renorm=True, scale=1.0,
+          ids=None, w=None, w_bf16=None):
+    """score -> (+bias) -> group-limited top-k -> normalise -> scale.  Returns (ids int32 [T,k], w fp32 [T,k])."""
+    _chk(logits, "logits", torch.float32)
+    T, E = logits.shape
+    if ids is None:
+        ids = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    if w is None:
+        w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    sf = L.SCORE_SOFTMAX if score_func == "softmax" else L.SCORE_SIGMOID
+    L.check(L.lib().b200moe_route(_ptr(ids), _ptr(w), _ptr(w_bf16), _ptr(logits), _ptr(bias), T, E, k, sf, n_groups,
+                                  topk_groups, int(renorm), float(scale), _stream()), "b200moe_route")
+    return ids, w
+
+
+def permute(ids, num_experts, status=None):
+    """Stable sort of the (token,slot) pairs by expert.  Returns (sorted_pair int32 [P], expert_offsets int32 [E+1])."""
+    _chk(ids, "ids", torch.int32)
+    T, k = ids.shape
+    P = T * k
+    sorted_pair = torch.empty(P, dtype=torch.int32, device=ids.device)
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=ids.device)
+    scratch = torch.empty(max(1, L.lib().b200moe_permute_scratch_ints(P, num_experts)), dtype=torch.int32,
+                          device=ids.device)
+    L.check(L.lib().b200moe_permute(_ptr(sorted_pair), _ptr(offsets), _ptr(ids), T, k, num_experts, _ptr(scratch),
+                                    _ptr(status), _stream()), "b200moe_permute")
+    return sorted_pair, offsets
+
+
+def gather_scatter_index(sorted_pair, offsets, T, k, num_experts):
+    dev = sorted_pair.device
+    gather = torch.full((num_experts, T), -1, dtype=torch.int32, device=dev)
+    scatter = torch.full((num_experts, T), -1, dtype=torch.int32, device=dev)
+    cnt = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    L.check(L.lib().b200moe_gather_scatter_index(_ptr(gather), _ptr(scatter), _ptr(cnt), _ptr(sorted_pair),
+                                                 _ptr(offsets), T, k, num_experts, _stream()),
+            "b200moe_gather_scatter_index")
+    return gather, scatter, cnt
+
+
+def quant_rows(x, row_map=None, div=1):
+    """Row gather + 1x128 e4m3 quantisation.  Returns (q e4m3 [rows,H], scales fp32 [H/128, ld]) - scales are stored
+    group-major with ld = rows rounded up to 128."""
+    _chk(x, "x", torch.bfloat16)
+    H = x.shape[1]
+    rows = row_map.numel() if row_map is not None else x.shape[0]
+    ld = (rows + 127) // 128 * 128
+    q = torch.empty(rows, H, dtype=torch.float8_e4m3fn, device=x.device)
+    s_t = torch.zeros(H // 128, ld, dtype=torch.float32, device=x.device)
+    L.check(L.lib().b200moe_quant_rows(_ptr(q), _ptr(s_t), ld, _ptr(x), _ptr(row_map), div, rows, H, _stream()),
+            "b200moe_quant_rows")
+    return q, s_t
+
+
+def make_desc(T, H, I, E, k, *, I_shared=0, out_mode=L.OUT_PER_SLOT, act_mode=L.ACT_W8A8, impl=L.IMPL_AUTO,
+              scale_dtype=torch.float32, w_dtype=torch.float32, reserved=0):
+    return L.ExpertsDesc(T, H, I, E, k, I_shared, out_mode, act_mode, impl, _DT[scale_dtype], _DT[w_dtype], reserved)
+
+
+def experts_workspace_bytes(desc):
+    return L.lib().b200moe_experts_workspace_bytes(ctypes.byref(desc))
+
+
+def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, act_mode=L.ACT_W8A8,
+            impl=L.IMPL_AUTO, workspace=None, status=None, reserved=0):
+    """Everything after routing (reference op my_ops.fused_moe_fused_experts, my_ops/fusedMoE.cpp:117-236).
+    ``out`` [T,k,H] -> un-weighted per-slot rows; ``out`` [T,H] -> weighted combine with ``topk_w`` (+ ``shared`` =
+    (wg,wu,wd,sg,su,sd) of a dense expert applied to every token).  Returns ``out``."""
+    _chk(out, "out", torch.bfloat16)
+    _chk(x, "x", torch.bfloat16)
+    for n, t in (("wg", wg), ("wu", wu), ("wd", wd)):
+        _chk(t, n, torch.float8_e4m3fn)
+    for n, t in (("sg", sg), ("su", su), ("sd", sd)):
+        _chk(t, n, sg.dtype)
+    _chk(ids, "ids", torch.int32)
+    T, H = x.shape
+    E, I, _ = wg.shape
+    k = ids.shape[1]
+    out_mode = L.OUT_PER_SLOT if out.dim() == 3 else L.OUT_COMBINED
+    I_shared = shared[0].shape[-2] if shared is not None else 0
+    d = make_desc(T, H, I, E, k, I_shared=I_shared, out_mode=out_mode, act_mode=act_mode, impl=impl,
+                  scale_dtype=sg.dtype, w_dtype=topk_w.dtype if topk_w is not None else torch.float32,
+                  reserved=reserved)
+    need = experts_workspace_bytes(d)
+    if need == 0 and T > 0:
+        raise ValueError("unsupported sizes for b200moe_experts (H, I multiples of 128; see include/b200moe.h)")
+    if workspace is None:
+        workspace = torch.empty(need + 256, dtype=torch.uint8, device=x.device)
+    base = (workspace.data_ptr() + 255) // 256 * 256
+    avail = workspace.numel() - (base - workspace.data_ptr())
+    sh = [_ptr(t) for t in shared] if shared is not None else [ctypes.c_void_p(0)] * 6
+    L.check(L.lib().b200moe_experts(_ptr(out), _ptr(x), _ptr(wg), _ptr(wu), _ptr(wd), _ptr(sg), _ptr(su), _ptr(sd),
+                                    _ptr(ids), _ptr(topk_w), *sh, ctypes.byref(d), ctypes.c_void_p(base), avail,
+                                    _ptr(status), _stream()), "b200moe_experts")
+    return out
+
+
+def combine(y, w, add=None, out=None):
+    _chk(y, "y", torch.bfloat16)
+    T, k, H = y.shape
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    L.check(L.lib().b200moe_combine(_ptr(out), _ptr(y), _ptr(w), _DT[w.dtype], _ptr(add), T, k, H, _stream()),
+            "b200moe_combine")
+    return out
