@@ -81,13 +81,13 @@ int b200moe_topk(void* values, int32_t* indices, const void* x, int dtype, int64
 int b200moe_router_logits(float* logits, const void* x, const void* wr, int64_t T, int64_t H,
                           int64_t E, void* stream);
 
-/* The rest of that chain in one kernel: score (softmax | sigmoid) -> (+bias, selection only) ->
+/* The rest of that chain in one kernel: (+logit_bias) -> score (softmax | sigmoid) -> (+bias, selection only) ->
  * group-limited top-k -> gather un-biased scores -> optional renormalisation -> * scale.
- * logits fp32 [T,E]; bias fp32 [E] or NULL; ids int32 [T,k]; w fp32 [T,k]; w_bf16 (optional) bf16
+ * logits fp32 [T,E]; logit_bias, bias fp32 [E] or NULL; ids int32 [T,k]; w fp32 [T,k]; w_bf16 (optional) bf16
  * [T,k].  n_groups <= 1 disables grouping.  Also the arithmetic behind
  * tpudnnFusedMoEGroupedTopkMultiCoreAsync (tpuDNNTensor.h:1572-1583). */
-int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits, const float* bias,
-                  int64_t T, int64_t E, int64_t k, int score_func, int64_t n_groups,
+int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits, const float* logit_bias,
+                  const float* bias, int64_t T, int64_t E, int64_t k, int score_func, int64_t n_groups,
                   int64_t topk_groups, int renorm, float scale, void* stream);
 
 /* ---- permutation ------------------------------------------------------------------------------ */
@@ -140,7 +140,8 @@ typedef struct {
   int impl;           /* B200MOE_IMPL_* */
   int scale_dtype;    /* B200MOE_F32 | B200MOE_BF16 */
   int w_dtype;        /* dtype of topk_w: B200MOE_F32 | B200MOE_BF16 */
-  int reserved;       /* 0; tests: bits 0-1 / 2-3 force the gate-up / down GEMM to 1 = simple, 2 = tcgen05 */
+  int reserved;       /* 0; tests: bits 0-1 / 2-3 force the gate-up / down GEMM to 1 = simple, 2 = tcgen05;
+                         profiling: bits 4..7 skip permute+quantise / gate-up GEMM / down GEMM / combine */
 } b200moe_experts_desc;
 
 size_t b200moe_experts_workspace_bytes(const b200moe_experts_desc* d);

@@ -146,6 +146,32 @@ def route_sigmoid_grouped(logits: torch.Tensor, bias: Optional[torch.Tensor], n_
     return ids.to(torch.int32), w
 
 
+def tie_free_rows(sel_scores: torch.Tensor, k: int, n_groups: int = 1, topk_groups: int = 1,
+                  rel_gap: float = 1e-6) -> torch.Tensor:
+    """Boolean mask of the rows whose selection is safe against ulp-level differences between exp
+    implementations: the k-th and (k+1)-th largest selection scores (after group masking) and, with groups,
+    the last kept and first dropped group score differ by more than ``rel_gap`` relative."""
+    s = sel_scores.to(torch.float64)
+    ok = torch.ones(s.shape[0], dtype=torch.bool)
+    if n_groups > 1:
+        g = s.view(s.shape[0], n_groups, -1)
+        gs = torch.sort(g, dim=-1, descending=True)[0][..., :2].sum(-1)
+        gv = torch.sort(gs, dim=-1, descending=True)[0]
+        if topk_groups < n_groups:
+            ok &= (gv[:, topk_groups - 1] - gv[:, topk_groups]) > rel_gap * gv[:, topk_groups - 1].abs().clamp_min(1e-30)
+        keep = torch.sort(gs, dim=-1, descending=True, stable=True)[1][:, :topk_groups]
+        mask = torch.ones(s.shape[0], n_groups, dtype=torch.bool).scatter_(1, keep, False)
+        s = g.masked_fill(mask.unsqueeze(-1), float("-inf")).reshape(s.shape[0], -1)
+    v = torch.sort(s, dim=-1, descending=True)[0]
+    if v.shape[-1] > k:
+        gap = v[:, k - 1] - v[:, k]
+        ok &= ~torch.isfinite(gap) | (gap > rel_gap * v[:, k - 1].abs().clamp_min(1e-30))
+    # ordering inside the top-k matters too (ids are compared position by position)
+    inner = v[:, :k - 1] - v[:, 1:k]
+    ok &= (inner > rel_gap * v[:, :k - 1].abs().clamp_min(1e-30)).all(-1)
+    return ok
+
+
 def assert_tie_free(sel_scores: torch.Tensor, k: int, rel_gap: float = 1e-6) -> None:
     """Generators call this: the k-th and (k+1)-th largest selection scores of every row
     must differ by more than ``rel_gap`` relative, so that ulp-level differences between

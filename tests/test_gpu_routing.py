@@ -78,20 +78,22 @@ def test_route_chain(ops, T, H, E, k, mode):
     torch.testing.assert_close(logits.cpu(), logits_cpu, rtol=1e-4, atol=1e-4)
     lg = logits.cpu()
     if mode == "softmax":
-        O.assert_tie_free(torch.softmax(lg, -1), k)
+        ok = O.tie_free_rows(torch.softmax(lg, -1), k)
         wid, ww = O.route_softmax_topk(lg, k)
         ids, w = ops.route(logits, k, "softmax")
     elif mode == "deepseek":
         bias = torch.randn(E, generator=torch.Generator().manual_seed(5)) * 0.01
-        O.assert_tie_free(torch.sigmoid(lg) + bias, k)
+        ok = O.tie_free_rows(torch.sigmoid(lg) + bias, k, 8, 4)
         wid, ww = O.route_sigmoid_grouped(lg, bias, 8, 4, k, 2.5)
         ids, w = ops.route(logits, k, "sigmoid", bias.to(DEV), 8, 4, True, 2.5)
     else:
-        O.assert_tie_free(torch.sigmoid(lg), k)
+        ok = O.tie_free_rows(torch.sigmoid(lg), k)
         wid, ww = O.route_sigmoid_grouped(lg, None, 1, 1, k, 1.0)
         ids, w = ops.route(logits, k, "sigmoid")
-    assert torch.equal(ids.cpu(), wid)
-    torch.testing.assert_close(w.cpu(), ww, rtol=1e-5, atol=1e-6)
+    # rows whose top-k boundary is closer than 1e-6 relative are not decidable across exp implementations
+    assert ok.float().mean() > 0.97
+    assert torch.equal(ids.cpu()[ok], wid[ok])
+    torch.testing.assert_close(w.cpu()[ok], ww[ok], rtol=1e-5, atol=1e-6)
 
 
 def test_invalid_arguments_are_rejected(ops):

@@ -89,6 +89,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
                                size_t workspace_bytes, int32_t* status, void* stream) {
   int rc = check_desc(d);
   if (rc != B200MOE_OK) return rc;
+  if (d->T == 0) return B200MOE_OK;  // nothing to do; empty tensors may carry null pointers
   MOE_CHECK_ARG(out && x && w_gate && w_up && w_down && s_gate && s_up && s_down && ids);
   if (d->out_mode == B200MOE_OUT_COMBINED) MOE_CHECK_ARG(topk_w);
   if (d->I_shared > 0)
@@ -96,7 +97,6 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   if (!moe_aligned16(out) || !moe_aligned16(x) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
       !moe_aligned16(w_down))
     return B200MOE_EALIGN;
-  if (d->T == 0) return B200MOE_OK;
   const WsLayout L = make_layout(*d);
   if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return B200MOE_EWORKSPACE;
@@ -111,12 +111,18 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   const int o1 = d->reserved & 3, o2 = (d->reserved >> 2) & 3;
   const bool tc1 = w8a8 && moe_tc_available() && (o1 ? o1 == 2 : use_tc);
   const bool tc2 = w8a8 && moe_tc_available() && (o2 ? o2 == 2 : use_tc);
+  // stage mask for profiling (a stage may be re-run alone on a workspace that a full call has filled):
+  // reserved bit 4 = skip permute/quantise, bit 5 = skip gate-up GEMM, bit 6 = skip down GEMM, bit 7 = skip combine
+  const bool do_prep = !(d->reserved & 16), do_g1 = !(d->reserved & 32), do_g2 = !(d->reserved & 64),
+             do_comb = !(d->reserved & 128);
 
-  rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
-  if (rc) return rc;
-  rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, st);
-  if (rc) return rc;
-  if (w8a8) {
+  if (do_prep) {
+    rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
+    if (rc) return rc;
+    rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, st);
+    if (rc) return rc;
+  }
+  if (w8a8 && do_prep) {
     rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.xq), reinterpret_cast<float*>(ws + L.xs), L.ld,
                             x, I32(L.sorted), d->k, L.P, d->H, stream);
     if (rc) return rc;
@@ -146,7 +152,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g.hs_t = reinterpret_cast<float*>(ws + L.hs);
   g.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.hq);
   g.status = status;
-  rc = tc1 ? moe_gemm1_tc(g, st) : moe_gemm1_simple(g, d->act_mode, st);
+  if (do_g1) rc = tc1 ? moe_gemm1_tc(g, st) : moe_gemm1_simple(g, d->act_mode, st);
   if (rc) return rc;
 
   MoeGemmArgs g2 = g;
@@ -158,16 +164,18 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g2.s0 = s_down;
   g2.s1 = nullptr;
   g2.out = reinterpret_cast<__nv_bfloat16*>(combined ? (void*)(ws + L.y) : out);
-  rc = tc2 ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, d->act_mode, st);
+  if (do_g2) rc = tc2 ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, d->act_mode, st);
   if (rc) return rc;
 
   const void* add = nullptr;
   if (d->I_shared > 0) {
-    rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, st);
-    if (rc) return rc;
-    rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, st);
-    if (rc) return rc;
-    if (w8a8) {
+    if (do_prep) {
+      rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, st);
+      if (rc) return rc;
+      rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, st);
+      if (rc) return rc;
+    }
+    if (w8a8 && do_prep) {
       rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.s_xq), reinterpret_cast<float*>(ws + L.s_xs),
                               L.lds, x, nullptr, 1, d->T, d->H, stream);
       if (rc) return rc;
@@ -192,7 +200,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     s.hq = reinterpret_cast<uint8_t*>(ws + L.s_hq);
     s.hs_t = reinterpret_cast<float*>(ws + L.s_hs);
     s.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.s_hq);
-    rc = tc1 ? moe_gemm1_tc(s, st) : moe_gemm1_simple(s, d->act_mode, st);
+    if (do_g1) rc = tc1 ? moe_gemm1_tc(s, st) : moe_gemm1_simple(s, d->act_mode, st);
     if (rc) return rc;
     MoeGemmArgs s2 = s;
     s2.aq = s.hq;
@@ -203,11 +211,11 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     s2.s0 = shared_s_down;
     s2.s1 = nullptr;
     s2.out = reinterpret_cast<__nv_bfloat16*>(ws + L.s_y);
-    rc = tc2 ? moe_gemm2_tc(s2, st) : moe_gemm2_simple(s2, d->act_mode, st);
+    if (do_g2) rc = tc2 ? moe_gemm2_tc(s2, st) : moe_gemm2_simple(s2, d->act_mode, st);
     if (rc) return rc;
     add = ws + L.s_y;
   }
-  if (combined) {
+  if (combined && do_comb) {
     rc = b200moe_combine(out, ws + L.y, topk_w, d->w_dtype, add, d->T, d->k, d->H, stream);
     if (rc) return rc;
   }

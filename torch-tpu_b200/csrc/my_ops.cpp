@@ -232,7 +232,7 @@ Tensor fused_moe_grouped_topk(Tensor& topk_experts_res, Tensor& topk_weights_res
   check_rc(b200moe_router_logits(matmul_res.data_ptr<float>(), left_bf16.data_ptr(), right_bf16.data_ptr(), T, H, E, st),
            "b200moe_router_logits");
   check_rc(b200moe_route(topk_experts_res.data_ptr<int32_t>(), topk_weights_res.data_ptr<float>(),
-                         topk_weights_res_bf16.data_ptr(), matmul_res.data_ptr<float>(), nullptr, T, E, k,
+                         topk_weights_res_bf16.data_ptr(), matmul_res.data_ptr<float>(), nullptr, nullptr, T, E, k,
                          B200MOE_SCORE_SOFTMAX, 1, 1, 1, 1.0f, st),
            "b200moe_route");
   return topk_experts_res;

@@ -133,8 +133,8 @@ topk_kernel(void* __restrict__ values, int32_t* __restrict__ indices, const void
 template <int VPT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 route_kernel(int32_t* __restrict__ ids, float* __restrict__ w, __nv_bfloat16* __restrict__ w_bf16,
-             const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int n, int k,
-             int score_func, int n_groups, int topk_groups, int renorm, float scale) {
+             const float* __restrict__ logits, const float* __restrict__ logit_bias,
+             const float* __restrict__ bias, int64_t T, int n, int k, int score_func, int n_groups, int topk_groups, int renorm, float scale) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= T) return;
@@ -143,7 +143,7 @@ route_kernel(int32_t* __restrict__ ids, float* __restrict__ w, __nv_bfloat16* __
 #pragma unroll
   for (int j = 0; j < VPT; ++j) {
     int e = lane + 32 * j;
-    s[j] = e < n ? logits[row * n + e] : -INFINITY;
+    s[j] = e < n ? (logit_bias ? logits[row * n + e] + logit_bias[e] : logits[row * n + e]) : -INFINITY;
   }
   if (score_func == B200MOE_SCORE_SOFTMAX) {
     float m = -INFINITY;
@@ -352,8 +352,8 @@ extern "C" int b200moe_topk(void* values, int32_t* indices, const void* x, int d
   return launch_topk(values, indices, x, dtype, batch, n, 1, 1, k, stream);
 }
 
-extern "C" int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits, const float* bias,
-                             int64_t T, int64_t E, int64_t k, int score_func, int64_t n_groups,
+extern "C" int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits,
+                             const float* logit_bias, const float* bias, int64_t T, int64_t E, int64_t k, int score_func, int64_t n_groups,
                              int64_t topk_groups, int renorm, float scale, void* stream) {
   MOE_CHECK_ARG(ids && w && logits && T >= 0 && E > 0 && k > 0);
   MOE_CHECK_ARG(score_func == B200MOE_SCORE_SOFTMAX || score_func == B200MOE_SCORE_SIGMOID);
@@ -366,7 +366,7 @@ extern "C" int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* 
   dim3 grid((unsigned)((T + kWarpsPerBlock - 1) / kWarpsPerBlock));
   return dispatch_vpt(E, [&](auto vpt) {
     route_kernel<decltype(vpt)::value><<<grid, kWarpsPerBlock * 32, 0, (cudaStream_t)stream>>>(
-        ids, w, reinterpret_cast<__nv_bfloat16*>(w_bf16), logits, bias, T, (int)E, (int)k, score_func,
+        ids, w, reinterpret_cast<__nv_bfloat16*>(w_bf16), logits, logit_bias, bias, T, (int)E, (int)k, score_func,
         (int)(n_groups > 1 ? n_groups : 1), (int)topk_groups, renorm, scale);
     return moe_launch_status();
   });

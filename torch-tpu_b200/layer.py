@@ -28,12 +28,12 @@ class MoEConfig:
 class FusedMoE:
     """One MoE layer on one GPU.  Weights are in the op layout: gate/up/down ``[E,I,H]`` float8_e4m3fn (down =
     W_down^T contiguous), scales ``[E,I/128,H/128]`` fp32 or bf16, router ``[E,H]`` bf16, optional selection bias
-    ``[E]`` fp32, optional shared expert ``(wg,wu,wd,sg,su,sd)`` with a leading dim of 1."""
+    ``[E]`` fp32 (added to the scores for selection only), optional ``logit_bias`` ``[E]`` fp32 (added to the logits), optional shared expert ``(wg,wu,wd,sg,su,sd)`` with a leading dim of 1."""
 
     def __init__(self, cfg: MoEConfig, router_w, wg, wu, wd, sg, su, sd, bias=None, shared: Optional[Tuple] = None,
-                 max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO):
+                 logit_bias=None, max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO):
         self.cfg = cfg
-        self.router_w, self.bias = router_w, bias
+        self.router_w, self.bias, self.logit_bias = router_w, bias, logit_bias
         self.w = (wg, wu, wd, sg, su, sd)
         self.shared = shared
         self.act_mode, self.impl = act_mode, impl
@@ -56,7 +56,7 @@ class FusedMoE:
         c = self.cfg
         logits = ops.router_logits(x, self.router_w, out=self.logits[:T])
         return ops.route(logits, c.top_k, c.score_func, self.bias, c.n_groups, c.topk_groups, c.renorm,
-                         c.routed_scale, ids=self.ids[:T], w=self.topk_w[:T])
+                         c.routed_scale, ids=self.ids[:T], w=self.topk_w[:T], logit_bias=self.logit_bias)
 
     def forward(self, x, out=None):
         """x bf16 [T,H] on the device -> bf16 [T,H] (a view of an internal buffer unless ``out`` is given)."""

@@ -33,7 +33,7 @@ SIGNATURES = {
                                       c_int64, c_void_p]),
     "b200moe_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p]),
     "b200moe_router_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
-    "b200moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
+    "b200moe_route": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                               c_int64, c_int64, c_int, c_float, c_void_p]),
     "b200moe_permute_scratch_ints": (c_size_t, [c_int64, c_int64]),
     "b200moe_permute": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,

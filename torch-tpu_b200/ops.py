@@ -61,8 +61,8 @@ def router_logits(x, wr, out=None):
 
 
 def route(logits, k, score_func="softmax", bias=None, n_groups=1, topk_groups=1, renorm=True, scale=1.0,
-          ids=None, w=None, w_bf16=None):
-    """score -> (+bias) -> group-limited top-k -> normalise -> scale.  Returns (ids int32 [T,k], w fp32 [T,k])."""
+          ids=None, w=None, w_bf16=None, logit_bias=None):
+    """(+logit_bias) -> score -> (+bias, selection only) -> group-limited top-k -> normalise -> scale.  Returns (ids int32 [T,k], w fp32 [T,k])."""
     _chk(logits, "logits", torch.float32)
     T, E = logits.shape
     if ids is None:
@@ -70,7 +70,7 @@ def route(logits, k, score_func="softmax", bias=None, n_groups=1, topk_groups=1,
     if w is None:
         w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
     sf = L.SCORE_SOFTMAX if score_func == "softmax" else L.SCORE_SIGMOID
-    L.check(L.lib().b200moe_route(_ptr(ids), _ptr(w), _ptr(w_bf16), _ptr(logits), _ptr(bias), T, E, k, sf, n_groups,
+    L.check(L.lib().b200moe_route(_ptr(ids), _ptr(w), _ptr(w_bf16), _ptr(logits), _ptr(logit_bias), _ptr(bias), T, E, k, sf, n_groups,
                                   topk_groups, int(renorm), float(scale), _stream()), "b200moe_route")
     return ids, w
 
