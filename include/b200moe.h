@@ -100,6 +100,20 @@ size_t b200moe_permute_scratch_ints(int64_t P, int64_t E);
 int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
                     int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream);
 
+/* b200moe_permute for callers that cannot hand over scratch memory.  No counterpart in the reference (its
+ * callers always pass scratch tensors in): it exists for hosts that must not allocate on the device around the
+ * call - a server with a memory pool fixed at start-up, a plugin that only receives input and output buffers.
+ * The chunk-count table lives in a fixed 256 KB array inside the library (held by every GPU that loads it, until
+ * the process exits); no cudaMalloc/cudaFree or other allocating routine is called.
+ * Limit: b200moe_permute_scratch_ints(T*k, E) <= b200moe_permute_static_max_scratch_ints() (65536; e.g. 262144
+ * pairs x 256 experts), otherwise B200MOE_ESHAPE.  The first call on each device looks up the array's device
+ * address; make that first call outside any stream capture.  All calls on a device share the one array: two calls
+ * whose kernels may overlap on the GPU (different streams) race - serialise them.  Nothing needs clearing
+ * between calls (the table is rewritten in full before it is read). */
+size_t b200moe_permute_static_max_scratch_ints(void);
+int b200moe_permute_static(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
+                           int64_t k, int64_t E, int32_t* status, void* stream);
+
 /* The reference's own scratch layout (fusedMoE.cpp:303-306, fusedMoE.pl:737-755): gather_index[E,T]
  * (token ids), scatter_index[E,T] (flat pair ids), num_per_expert[E]; unused tail entries are left
  * untouched.  Computed from sorted_pair / expert_offsets. */

@@ -239,3 +239,46 @@ extern "C" int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void
       q, s_t, ld, reinterpret_cast<const __nv_bfloat16*>(x), row_map, (int)div, rows, (int)H);
   return moe_launch_status();
 }
+
+// ---- permutation without caller-provided scratch ---------------------------------------------------
+// For hosts that must not (or cannot) allocate device memory around the call - a serving process whose
+// memory pool is fixed at start-up, code running inside a stream capture, a plugin that is only handed
+// input and output buffers.  The chunk-count table that b200moe_permute takes from the caller lives here in
+// a fixed array inside the library image instead; every GPU that loads the library holds these 256 KB until
+// the process exits.
+constexpr size_t kStaticScratchInts = 64 * 1024;  // 256 KB: e.g. 65536 pairs x 1024 experts, 262144 pairs x 256
+static __device__ __align__(256) int32_t g_permute_scratch[kStaticScratchInts];
+
+namespace {
+// In host code `g_permute_scratch` is only a handle for the runtime, not a device address, so the address the
+// kernels need is looked up once per device, with that device current.
+int static_scratch_ptr(int32_t** out) {
+  constexpr int kMaxDevices = 64;
+  static int32_t* ptrs[kMaxDevices] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return B200MOE_ESHAPE;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_permute_scratch);
+    if (e != cudaSuccess) return (int)e;
+    ptrs[dev] = reinterpret_cast<int32_t*>(p);
+  }
+  *out = ptrs[dev];
+  return B200MOE_OK;
+}
+}  // namespace
+
+extern "C" size_t b200moe_permute_static_max_scratch_ints(void) { return kStaticScratchInts; }
+
+extern "C" int b200moe_permute_static(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids,
+                                      int64_t T, int64_t k, int64_t E, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(T >= 0 && k > 0 && E > 0);
+  if (b200moe_permute_scratch_ints(T * k, E) > kStaticScratchInts) return B200MOE_ESHAPE;
+  int32_t* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc != B200MOE_OK) return rc;
+  // The table is written in full by the histogram step before it is read, so nothing has to be cleared.
+  return b200moe_permute(sorted_pair, expert_offsets, ids, T, k, E, scratch, status, stream);
+}

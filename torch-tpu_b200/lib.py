@@ -38,6 +38,8 @@ SIGNATURES = {
     "b200moe_permute_scratch_ints": (c_size_t, [c_int64, c_int64]),
     "b200moe_permute": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                 c_void_p]),
+    "b200moe_permute_static_max_scratch_ints": (c_size_t, []),
+    "b200moe_permute_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "b200moe_gather_scatter_index": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                              c_int64, c_void_p]),
     "b200moe_quant_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int64,
