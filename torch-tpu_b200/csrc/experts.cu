@@ -9,7 +9,7 @@ namespace {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct WsLayout {
-  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y;
+  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32;
   size_t s_offsets, s_mtiles, s_nmt, s_xq, s_xs, s_hq, s_hs, s_y;
   size_t total;
   int64_t P, ld, lds;
@@ -42,6 +42,8 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   L.hq = take(w8a8 ? (size_t)P * d.I : (size_t)P * d.I * 2);
   L.hs = take(w8a8 ? nI * (size_t)L.ld * sizeof(float) : 0);
   L.y = take(d.out_mode == B200MOE_OUT_COMBINED ? (size_t)P * d.H * 2 : 0);
+  // fp32 copies of bf16 block scales (the tensor-core kernels read fp32 scales only)
+  L.sc32 = take(d.scale_dtype == B200MOE_BF16 && w8a8 ? 3 * (size_t)d.E * nI * nH * sizeof(float) : 0);
   if (d.I_shared > 0) {
     const size_t nIs = d.I_shared / kBlock;
     L.s_offsets = take(2 * sizeof(int32_t));
@@ -52,9 +54,20 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
     L.s_hq = take(w8a8 ? (size_t)d.T * d.I_shared : (size_t)d.T * d.I_shared * 2);
     L.s_hs = take(w8a8 ? nIs * (size_t)L.lds * sizeof(float) : 0);
     L.s_y = take((size_t)d.T * d.H * 2);
+    L.s_sc32 = take(d.scale_dtype == B200MOE_BF16 && w8a8 ? 3 * nIs * nH * sizeof(float) : 0);
   }
   L.total = o;
   return L;
+}
+
+__global__ void scales_to_f32_kernel(float* __restrict__ dst, const __nv_bfloat16* __restrict__ a,
+                                     const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ c, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    dst[i] = __bfloat162float(a[i]);
+    dst[n + i] = __bfloat162float(b[i]);
+    dst[2 * n + i] = __bfloat162float(c[i]);
+  }
 }
 
 int check_desc(const b200moe_experts_desc* d) {
@@ -128,6 +141,17 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     if (rc) return rc;
   }
 
+  const bool cvt = d->scale_dtype == B200MOE_BF16 && (tc1 || tc2);
+  const int64_t nsc = d->E * (d->I / kBlock) * (d->H / kBlock);
+  if (cvt && do_prep) {
+    scales_to_f32_kernel<<<(unsigned)((nsc + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<float*>(ws + L.sc32), reinterpret_cast<const __nv_bfloat16*>(s_gate),
+        reinterpret_cast<const __nv_bfloat16*>(s_up), reinterpret_cast<const __nv_bfloat16*>(s_down), nsc);
+    rc = moe_launch_status();
+    if (rc) return rc;
+  }
+  const float* sc32 = reinterpret_cast<const float*>(ws + L.sc32);
+
   MoeGemmArgs g{};
   g.aq = reinterpret_cast<const uint8_t*>(ws + L.xq);
   g.as_t = reinterpret_cast<const float*>(ws + L.xs);
@@ -152,7 +176,15 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g.hs_t = reinterpret_cast<float*>(ws + L.hs);
   g.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.hq);
   g.status = status;
-  if (do_g1) rc = tc1 ? moe_gemm1_tc(g, st) : moe_gemm1_simple(g, d->act_mode, st);
+  if (do_g1) {
+    if (tc1) {
+      MoeGemmArgs t = g;
+      if (cvt) t.s0 = sc32, t.s1 = sc32 + nsc, t.scale_dtype = B200MOE_F32;
+      rc = moe_gemm1_tc(t, st);
+    } else {
+      rc = moe_gemm1_simple(g, d->act_mode, st);
+    }
+  }
   if (rc) return rc;
 
   MoeGemmArgs g2 = g;
@@ -164,7 +196,15 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g2.s0 = s_down;
   g2.s1 = nullptr;
   g2.out = reinterpret_cast<__nv_bfloat16*>(combined ? (void*)(ws + L.y) : out);
-  if (do_g2) rc = tc2 ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, d->act_mode, st);
+  if (do_g2) {
+    if (tc2) {
+      MoeGemmArgs t = g2;
+      if (cvt) t.s0 = sc32 + 2 * nsc, t.scale_dtype = B200MOE_F32;
+      rc = moe_gemm2_tc(t, st);
+    } else {
+      rc = moe_gemm2_simple(g2, d->act_mode, st);
+    }
+  }
   if (rc) return rc;
 
   const void* add = nullptr;
@@ -180,6 +220,16 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
                               L.lds, x, nullptr, 1, d->T, d->H, stream);
       if (rc) return rc;
     }
+    const int64_t nscs = (d->I_shared / kBlock) * (d->H / kBlock);
+    if (cvt && do_prep) {
+      scales_to_f32_kernel<<<(unsigned)((nscs + 255) / 256), 256, 0, st>>>(
+          reinterpret_cast<float*>(ws + L.s_sc32), reinterpret_cast<const __nv_bfloat16*>(shared_s_gate),
+          reinterpret_cast<const __nv_bfloat16*>(shared_s_up), reinterpret_cast<const __nv_bfloat16*>(shared_s_down),
+          nscs);
+      rc = moe_launch_status();
+      if (rc) return rc;
+    }
+    const float* ssc32 = reinterpret_cast<const float*>(ws + L.s_sc32);
     MoeGemmArgs s = g;
     s.aq = reinterpret_cast<const uint8_t*>(ws + L.s_xq);
     s.as_t = reinterpret_cast<const float*>(ws + L.s_xs);
@@ -200,7 +250,15 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     s.hq = reinterpret_cast<uint8_t*>(ws + L.s_hq);
     s.hs_t = reinterpret_cast<float*>(ws + L.s_hs);
     s.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.s_hq);
-    if (do_g1) rc = tc1 ? moe_gemm1_tc(s, st) : moe_gemm1_simple(s, d->act_mode, st);
+    if (do_g1) {
+      if (tc1) {
+        MoeGemmArgs t = s;
+        if (cvt) t.s0 = ssc32, t.s1 = ssc32 + nscs, t.scale_dtype = B200MOE_F32;
+        rc = moe_gemm1_tc(t, st);
+      } else {
+        rc = moe_gemm1_simple(s, d->act_mode, st);
+      }
+    }
     if (rc) return rc;
     MoeGemmArgs s2 = s;
     s2.aq = s.hq;
@@ -211,7 +269,15 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     s2.s0 = shared_s_down;
     s2.s1 = nullptr;
     s2.out = reinterpret_cast<__nv_bfloat16*>(ws + L.s_y);
-    if (do_g2) rc = tc2 ? moe_gemm2_tc(s2, st) : moe_gemm2_simple(s2, d->act_mode, st);
+    if (do_g2) {
+      if (tc2) {
+        MoeGemmArgs t = s2;
+        if (cvt) t.s0 = ssc32 + 2 * nscs, t.scale_dtype = B200MOE_F32;
+        rc = moe_gemm2_tc(t, st);
+      } else {
+        rc = moe_gemm2_simple(s2, d->act_mode, st);
+      }
+    }
     if (rc) return rc;
     add = ws + L.s_y;
   }

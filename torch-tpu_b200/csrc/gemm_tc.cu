@@ -8,8 +8,9 @@
 //   gemm2  y = h Wd                      per expert, rows scattered to their (token,slot) position
 //          (my_ops/fusedMoE.pl:264-269 + scatter_store :55-96)
 //
-// One persistent CTA per SM, 10 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and TMEM
-// owner, warps 2..9 = epilogue (TMEM lane quarter = warp%4, column half = (warp-2)/4).
+// One persistent CTA per SM, 12 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and TMEM
+// owner, warps 2-3 idle (they only give their registers away), warps 4..11 = epilogue (TMEM lane quarter =
+// warp%4, column half = (warp-4)/4).  setmaxnreg moves registers from the first warpgroup to the epilogue.
 // A tile is 128 rows x 256 MMA columns: gemm1 -> 128 gate + 128 up columns of one 128-wide slice of I
 // (so SiLU*up and the 1x128 requantisation stay inside the CTA); gemm2 -> 256 columns of H.
 // Weights keep the reference layout [E,I,H]: for gemm1 the B operand is K-major, for gemm2 (K = I is the
@@ -18,12 +19,13 @@
 // No multicast loads anywhere.  Every wait is bounded: on a time-out the CTA raises status bit 1, all roles
 // leave their loops, tensor memory is released and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include "internal.h"
 
 namespace {
 
-constexpr int TC_THREADS = 320;
+constexpr int TC_THREADS = 384;  // three warpgroups: {producer, MMA, 2 idle}, 2 x 4 epilogue warps
 constexpr int TC_STAGES = 4;
 constexpr int TC_A_BYTES = 128 * 128;       // 128 rows x 128 B
 constexpr int TC_B_BYTES = 2 * 128 * 128;   // two 128 x 128 B boxes
@@ -33,8 +35,8 @@ constexpr uint32_t TC_SPIN_LIMIT = 4u << 20;  // polls (with back-off) before a 
 
 struct TcShared {
   uint64_t full[TC_STAGES];
-  uint64_t empty[TC_STAGES];
-  uint64_t tmem_full[2];
+  uint64_t empty[TC_STAGES];  // MMAs of the stage's K block are complete: the stage may be refilled AND the block's
+                              // accumulator buffer may be read (one tcgen05.commit per K block serves both)
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
@@ -42,12 +44,37 @@ struct TcShared {
 };
 constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
 
+// Optional per-role cycle accounting (compile with -DMOE_TC_PROFILE): slot[blockIdx.x*8 + i]
+//   0 producer wait(empty)  1 mma wait(full)  2 mma wait(tmem_empty)  3 mma total
+//   4 epilogue wait(tmem_full)  5 epilogue wake->buffer released  6 epilogue rest (FMAs after release, tile end)
+//   7 epilogue total  8 first two TMEM loads  9 FMAs + two more loads + wait  10 unused  11 fence + release
+#ifdef MOE_TC_PROFILE
+__device__ long long g_tc_prof[256 * 12];
+#define PROF_DECL(v) long long v = 0
+#define PROF_T0(t) long long t = clock64()
+#define PROF_ADD(v, t) v += clock64() - t
+#define PROF_STORE(i, v) if (blockIdx.x < 256) g_tc_prof[blockIdx.x * 12 + (i)] = (v)
+#else
+#define PROF_DECL(v)
+#define PROF_T0(t)
+#define PROF_ADD(v, t)
+#define PROF_STORE(i, v)
+#endif
+// Ablation switches for timing experiments (compile with -DMOE_TC_ABLATE, select with env MOE_TC_DBG):
+// bit 0 skip FMAs, bit 1 constant scales, bit 2 skip tile end, bit 3 skip TMEM loads, bit 4 skip the B-operand
+// copies, bit 5 skip the MMAs, bit 6 skip all operand copies
+#if defined(MOE_TC_PROFILE) || defined(MOE_TC_ABLATE)
+#define MOE_TC_DBG_ON 1
+#define DBG(bit) ((a.dbg >> (bit)) & 1)
+#else
+#define DBG(bit) false
+#endif
+
 struct TcArgs {
   const float* as_t;
   int64_t ld;
   const void* s0;
   const void* s1;
-  int scale_dtype;
   const int32_t* mtiles;
   const int32_t* num_mtiles;
   const int32_t* offsets;
@@ -57,6 +84,7 @@ struct TcArgs {
   float* hs_t;
   __nv_bfloat16* out;
   int32_t* status;
+  int dbg;  // MOE_TC_PROFILE / MOE_TC_ABLATE builds only: bit 0 skip FMAs, bit 1 constant scales, bit 2 skip tile end
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------
@@ -116,14 +144,13 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread, completed before returning
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
+// issue only; the destination registers are valid after tc_ld_wait2 on them
+__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-      "tcgen05.wait::ld.sync.aligned;"
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
@@ -131,6 +158,45 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// wait for every outstanding tcgen05.ld; the two register sets are in/out operands so that no use of them can be
+// scheduled above the wait
+__device__ __forceinline__ void tc_ld_wait2(uint32_t (&a)[32], uint32_t (&b)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
+                 "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
+                 "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]), "+r"(a[23]),
+                 "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]), "+r"(a[30]), "+r"(a[31]),
+                 "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
+                 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]),
+                 "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]),
+                 "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
+               :
+               : "memory");
+}
+// packed fp32 pairs: one fma.rn.f32x2 does two multiply-adds with one instruction slot
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ float2 unpack2(uint64_t v) {
+  float2 r;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+  return r;
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// SiLU with the fast exponential and reciprocal (ex2.approx / rcp.approx): relative error ~1e-6, far inside the
+// rounding of the e4m3 requantisation that follows
+__device__ __forceinline__ float moe_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand tile (8-row x 128-byte atoms, 1024 B each).
 //   K-major : rows are M/N indices, 128 B of K per row; SBO = 1024 (next 8 rows); LBO unused (1)
@@ -163,7 +229,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       mbar_init(smem_u32(&sh->empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
       mbar_init(smem_u32(&sh->tmem_empty[b]), 8);
     }
     sh->abort_flag = 0;
@@ -185,25 +250,34 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int KB = (GEMM2 ? a.I : a.H) / kBlock;
   const int nH = a.H / kBlock, nI = a.I / kBlock;
 
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      PROF_DECL(p_wait);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
         const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % TC_STAGES;
           const uint32_t ph = (it / TC_STAGES) & 1;
+          PROF_T0(tw);
           if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
+          PROF_ADD(p_wait, tw);
           const uint32_t full = smem_u32(&sh->full[s]);
           const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-          mbar_arrive_expect_tx(full, TC_STAGE_BYTES);
+          if (DBG(6)) {  // no copies at all: the MMAs run on whatever the stage holds
+            mbar_arrive(full);
+            continue;
+          }
+          mbar_arrive_expect_tx(full, DBG(4) ? TC_A_BYTES : TC_STAGE_BYTES);
           tma_load_2d(sa, &tmA, kb * kBlock, row0, full);
+          if (DBG(4)) continue;
           if (!GEMM2) {
             tma_load_2d(sb, &tmB0, kb * kBlock, e * a.I + nt * 128, full);
             tma_load_2d(sb + 128 * 128, &tmB1, kb * kBlock, e * a.I + nt * 128, full);
@@ -213,6 +287,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
         }
       }
+      PROF_STORE(0, p_wait);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
@@ -220,17 +295,27 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const uint32_t idesc = make_idesc(GEMM2 ? 1 : 0);
       uint32_t it = 0;
       bool ok = true;
+      PROF_DECL(m_wfull);
+      PROF_DECL(m_wtmem);
+      PROF_T0(m_t0);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % TC_STAGES;
           const uint32_t ph = (it / TC_STAGES) & 1;
           const int buf = it & 1;
           const uint32_t bph = (it >> 1) & 1;
-          if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag) ||
-              !mbar_wait(smem_u32(&sh->tmem_empty[buf]), bph ^ 1, abort_flag)) {
+          PROF_T0(tw1);
+          if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) {
             ok = false;
             break;
           }
+          PROF_ADD(m_wfull, tw1);
+          PROF_T0(tw2);
+          if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), bph ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          PROF_ADD(m_wtmem, tw2);
           tc_fence_after();
           const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
           const uint64_t adesc = make_smem_desc(sa, 16, 1024);
@@ -241,80 +326,146 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             // K advances 32 elements: +32 B inside the swizzle atom (K-major) or +32 rows of 128 B (MN-major)
             const uint64_t ad = adesc + (uint64_t)(ks * 2);
             const uint64_t bd = bdesc + (uint64_t)(GEMM2 ? ks * 256 : ks * 2);
-            tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
+            if (!DBG(5)) tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
           }
-          tc_commit(smem_u32(&sh->empty[s]));
-          tc_commit(smem_u32(&sh->tmem_full[buf]));
+          tc_commit(smem_u32(&sh->empty[s]));  // wakes the producer (refill) and the epilogue (accumulator ready)
         }
       }
+      PROF_DECL(m_total);
+      PROF_ADD(m_total, m_t0);
+      PROF_STORE(1, m_wfull);
+      PROF_STORE(2, m_wtmem);
+      PROF_STORE(3, m_total);
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue (8 warps)
-    const int q = warp & 3, hlf = (warp - 2) >> 2;
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue (8 warps, 232 registers each)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    const int q = warp & 3, hlf = (warp - 4) >> 2;
     const int rit = q * 32 + lane;  // row inside the tile == TMEM lane
     uint32_t it = 0;
     bool ok = true;
+    PROF_DECL(e_wait);
+    PROF_DECL(e_ld);
+    PROF_DECL(e_end);
+    PROF_DECL(e_s1);
+    PROF_DECL(e_s2);
+    PROF_DECL(e_s3);
+    PROF_DECL(e_s4);
+    PROF_T0(e_t0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
       const int row_end = a.offsets[e + 1];
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
-      float acc[2][64];
+      // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's 64-column span of half j
+      uint64_t acc[2][32];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int i = 0; i < 64; ++i) acc[j][i] = 0.f;
-      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]
-      const int64_t sbase = GEMM2 ? (int64_t)e * nI * nH + 2 * nt : ((int64_t)e * nI + nt) * nH;
-      const int64_t sstep = GEMM2 ? nH : 1;
-      const bool j1_in = GEMM2 ? (2 * nt + 1 < nH) : true;
-      float sa_n = valid ? a.as_t[grow] : 0.f;
-      float w0_n = moe_load_as_f32(a.s0, sbase, a.scale_dtype);
-      float w1_n = GEMM2 ? (j1_in ? moe_load_as_f32(a.s0, sbase + 1, a.scale_dtype) : 0.f)
-                         : moe_load_as_f32(a.s1, sbase, a.scale_dtype);
+        for (int i = 0; i < 32; ++i) acc[j][i] = 0ull;
+      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here
+      const float* __restrict__ ws0 = reinterpret_cast<const float*>(a.s0) + (GEMM2 ? (int64_t)e * nI * nH + 2 * nt
+                                                                                   : ((int64_t)e * nI + nt) * nH);
+      const float* __restrict__ ws1 = GEMM2 ? ws0 + ((2 * nt + 1 < nH) ? 1 : 0)
+                                            : reinterpret_cast<const float*>(a.s1) + ((int64_t)e * nI + nt) * nH;
+      const int sstep = GEMM2 ? nH : 1;
+      const float* __restrict__ sap = a.as_t + grow;
+      // scales are fetched three K blocks ahead (the activation-scale lines come from L2)
+      float sa0 = valid ? sap[0] : 0.f, sa1 = (valid && KB > 1) ? sap[a.ld] : 0.f,
+            sa2 = (valid && KB > 2) ? sap[2 * a.ld] : 0.f;
+      float wa0 = ws0[0], wa1 = KB > 1 ? ws0[sstep] : 0.f, wa2 = KB > 2 ? ws0[2 * sstep] : 0.f;
+      float wb0 = ws1[0], wb1 = KB > 1 ? ws1[sstep] : 0.f, wb2 = KB > 2 ? ws1[2 * sstep] : 0.f;
       for (int kb = 0; kb < KB; ++kb, ++it) {
-        const float f0 = sa_n * w0_n, f1 = sa_n * w1_n;
-        if (kb + 1 < KB) {  // prefetch the next block's scales while this block's MMAs run
-          sa_n = valid ? a.as_t[(int64_t)(kb + 1) * a.ld + grow] : 0.f;
-          w0_n = moe_load_as_f32(a.s0, sbase + (kb + 1) * sstep, a.scale_dtype);
-          w1_n = GEMM2 ? (j1_in ? moe_load_as_f32(a.s0, sbase + (kb + 1) * sstep + 1, a.scale_dtype) : 0.f)
-                       : moe_load_as_f32(a.s1, sbase + (kb + 1) * sstep, a.scale_dtype);
+        const float f0 = DBG(1) ? 1.f : sa0 * wa0, f1 = DBG(1) ? 1.f : sa0 * wb0;
+        sa0 = sa1, sa1 = sa2, wa0 = wa1, wa1 = wa2, wb0 = wb1, wb1 = wb2;
+        if (kb + 3 < KB && !DBG(1)) {
+          sa2 = valid ? sap[(int64_t)(kb + 3) * a.ld] : 0.f;
+          wa2 = ws0[(kb + 3) * sstep];
+          wb2 = ws1[(kb + 3) * sstep];
         }
         const int buf = it & 1;
-        const uint32_t bph = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&sh->tmem_full[buf]), bph, abort_flag)) {
+        PROF_T0(tw);
+        if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
           ok = false;
           break;
         }
+        PROF_ADD(e_wait, tw);
+        PROF_T0(tl);
         tc_fence_after();
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hlf * 64;
+        const uint64_t f0p = pack2(f0, f0), f1p = pack2(f1, f1);
+        uint32_t s0[32], s1[32];
+#ifdef MOE_TC_DBG_ON
+        if (DBG(3)) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            float v[32];
-            tc_ld32(tbase + j * 128 + c * 32, v);
-            if (j == 1 && c == 1) {  // all four chunks are in registers: hand the buffer back
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
-            }
-            const float f = j == 0 ? f0 : f1;
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[j][c * 32 + i] = fmaf(v[i], f, acc[j][c * 32 + i]);
-          }
+          for (int i = 0; i < 32; ++i) s0[i] = s1[i] = 0;
         }
+        if (!DBG(3)) {
+#endif
+        tc_ld32_issue(tbase, s0);            // half 0, columns 0..31 of the span
+        tc_ld32_issue(tbase + 32, s1);       // half 0, columns 32..63
+        tc_ld_wait2(s0, s1);
+#ifdef MOE_TC_DBG_ON
+        }
+#endif
+        PROF_ADD(e_s1, tl);
+        PROF_T0(t2);
+#ifdef MOE_TC_DBG_ON
+        if (!DBG(0))
+#endif
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[0][i] = ffma2(pack2u(s0[2 * i], s0[2 * i + 1]), f0p, acc[0][i]);
+#ifdef MOE_TC_DBG_ON
+        if (!DBG(3))
+#endif
+        tc_ld32_issue(tbase + 128, s0);      // half 1, columns 0..31
+#ifdef MOE_TC_DBG_ON
+        if (!DBG(0))
+#endif
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[0][16 + i] = ffma2(pack2u(s1[2 * i], s1[2 * i + 1]), f0p, acc[0][16 + i]);
+#ifdef MOE_TC_DBG_ON
+        if (!DBG(3)) {
+#endif
+        tc_ld32_issue(tbase + 128 + 32, s1); // half 1, columns 32..63
+        tc_ld_wait2(s0, s1);
+#ifdef MOE_TC_DBG_ON
+        }
+#endif
+        PROF_ADD(e_s2, t2);
+        PROF_T0(t4);
+        tc_fence_before();                   // all of this block is in registers: hand the buffer back
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+        PROF_ADD(e_s4, t4);
+        PROF_ADD(e_ld, tl);
+        PROF_T0(tp);
+#ifdef MOE_TC_DBG_ON
+        if (!DBG(0)) {
+#endif
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[1][i] = ffma2(pack2u(s0[2 * i], s0[2 * i + 1]), f1p, acc[1][i]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[1][16 + i] = ffma2(pack2u(s1[2 * i], s1[2 * i + 1]), f1p, acc[1][16 + i]);
+#ifdef MOE_TC_DBG_ON
+        }
+#endif
+        PROF_ADD(e_end, tp);
       }
       if (!ok) break;
+      PROF_T0(te);
+      if (DBG(2)) continue;
       if (!GEMM2) {
         // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over two warps
+        float h[64];
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const float h = moe_silu(acc[0][i]) * acc[1][i];
-          acc[0][i] = h;
-          amax = fmaxf(amax, fabsf(h));
+        for (int i = 0; i < 32; ++i) {
+          const float2 g = unpack2(acc[0][i]), u = unpack2(acc[1][i]);
+          h[2 * i] = moe_silu_fast(g.x) * u.x;
+          h[2 * i + 1] = moe_silu_fast(g.y) * u.y;
+          amax = fmaxf(amax, fmaxf(fabsf(h[2 * i]), fabsf(h[2 * i + 1])));
         }
         sh->amax[hlf][rit] = amax;
         asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -330,8 +481,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
               const int i = v4 * 16 + w * 4;
-              ow[w] = moe_f32x4_to_e4m3x4(acc[0][i] * inv, acc[0][i + 1] * inv, acc[0][i + 2] * inv,
-                                          acc[0][i + 3] * inv);
+              ow[w] = moe_f32x4_to_e4m3x4(h[i] * inv, h[i + 1] * inv, h[i + 2] * inv, h[i + 3] * inv);
             }
             dst[v4] = o;
           }
@@ -349,13 +499,28 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               uint4 o;
               __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-              for (int w = 0; w < 4; ++w)
-                o2[w] = __floats2bfloat162_rn(acc[j][v4 * 8 + 2 * w], acc[j][v4 * 8 + 2 * w + 1]);
+              for (int w = 0; w < 4; ++w) {
+                const float2 v = unpack2(acc[j][v4 * 4 + w]);
+                o2[w] = __floats2bfloat162_rn(v.x, v.y);
+              }
               dst[v4] = o;
             }
           }
         }
       }
+      PROF_ADD(e_end, te);
+    }
+    if (warp == 4 && lane == 0) {
+      PROF_DECL(e_total);
+      PROF_ADD(e_total, e_t0);
+      PROF_STORE(4, e_wait);
+      PROF_STORE(5, e_ld);
+      PROF_STORE(6, e_end);
+      PROF_STORE(7, e_total);
+      PROF_STORE(8, e_s1);
+      PROF_STORE(9, e_s2);
+      PROF_STORE(10, e_s3);
+      PROF_STORE(11, e_s4);
     }
   }
 
@@ -416,6 +581,7 @@ int device_sm_count() {
 
 template <bool GEMM2>
 int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
+  if (g.scale_dtype != B200MOE_F32) return B200MOE_EINVAL;  // the caller converts bf16 scales first
   const int K = GEMM2 ? g.I : g.H;
   CUtensorMap tmA, tmB0, tmB1;
   if (!make_map_u8(&tmA, g.aq, (uint64_t)g.P, (uint64_t)K)) return B200MOE_EDRIVER;
@@ -426,7 +592,6 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.ld = g.ld;
   a.s0 = g.s0;
   a.s1 = g.s1;
-  a.scale_dtype = g.scale_dtype;
   a.mtiles = g.mtiles;
   a.num_mtiles = g.num_mtiles;
   a.offsets = g.offsets;
@@ -438,6 +603,9 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.hs_t = g.hs_t;
   a.out = g.out;
   a.status = g.status;
+#ifdef MOE_TC_DBG_ON
+  a.dbg = getenv("MOE_TC_DBG") ? atoi(getenv("MOE_TC_DBG")) : 0;
+#endif
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
@@ -451,6 +619,12 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
 }
 
 }  // namespace
+
+#ifdef MOE_TC_PROFILE
+extern "C" int b200moe_debug_read_tc_profile(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(long long) * 256 * 12);
+}
+#endif
 
 bool moe_tc_available() {
   static bool ok = [] {
