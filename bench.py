@@ -150,8 +150,14 @@ def time_steps(fn, steps, warmup, barrier=None):
     return e0.elapsed_time(e1) / steps  # ms per step
 
 
-def launches_per_step(wl, T):
+def launches_per_step(wl, T, world=1):
     P = T * wl["k"]
+    if world > 1:
+        # router, route, permute, pack | unpack ids, permute (received rows), unpack rows, tiles, 2 GEMMs | invert, combine
+        n = 2 + (1 if P <= 1024 else 3) + 1 + 1 + 3 + 1 + 1 + 2 + 2
+        if wl.get("shared"):
+            n += (1 if T <= 1024 else 3) + 1 + 1 + 2      # permute (identity ids), tiles, quant, 2 GEMMs
+        return n
     n = 2 + (1 if P <= 1024 else 3) + 1 + 1 + 2 + 1   # router, route, permute, tiles, quant, 2 GEMMs, combine
     if wl.get("shared"):
         n += 2 + 1 + 2                                  # identity offsets + tiles, quant, 2 GEMMs
@@ -275,7 +281,7 @@ def main():
     with ClockSampler(local) as cs:
         ms = time_steps(step, args.steps, args.warmup, barrier)
     clocks = cs.summary()
-    status = int(layer.status.item())
+    status = int((layer.layer if world > 1 else layer).status.item())
 
     # ---- end to end with host buffers ---------------------------------------------------------------------------
     xh = [x.cpu().pin_memory() for x in xs]
@@ -302,7 +308,7 @@ def main():
                        "l2": "weights >> 126 MB L2, 4 rotating input batches"},
             "e2e": {"value": T * world / (ms_e2e / 1000), "unit": "tokens/s", "h2d_bytes_per_step": T * wl["H"] * 2,
                     "d2h_bytes_per_step": T * wl["H"] * 2},
-            "gpu_launches": launches_per_step(wl, T) * args.steps, "clocks": clocks, "device_status": status}
+            "gpu_launches": launches_per_step(wl, T, world) * args.steps, "clocks": clocks, "device_status": status}
 
     if rank == 0 and world == 1:
         # ---- roofline of the dominant kernel: gate/up GEMM alone on the filled workspace ---------------------------
@@ -348,14 +354,16 @@ def main():
                 xx = [make_x(Ts, wl["H"], dev, seed=300 + i).to(dev) for i in range(4)]
                 j = [0]
 
+                use_graph = Ts <= 64   # decode sizes: one graph launch instead of a dozen small ones
+
                 def st():
-                    layer.forward(xx[j[0] % 4])
+                    (layer.forward_graph if use_graph else layer.forward)(xx[j[0] % 4])
                     j[0] += 1
                 m = time_steps(st, max(args.steps, 30), 5)
                 ea = int(torch.unique(layer.ids[:Ts]).numel())
                 fl, nb = algorithmic(wl, Ts, ea)
                 t_tc, t_hbm = fl / (fp8_peak * 1e12), nb / (peaks["hbm"] * 1e9)
-                sweep.append({"tokens": Ts, "ms_per_step": m, "tokens_per_s": Ts / (m / 1000),
+                sweep.append({"tokens": Ts, "cuda_graph": use_graph, "ms_per_step": m, "tokens_per_s": Ts / (m / 1000),
                               "bound": "tensor" if t_tc >= t_hbm else "hbm", "activated_experts": ea,
                               "frac": (fl / (m / 1000) / 1e12 / fp8_peak) if t_tc >= t_hbm else
                               (nb / (m / 1000) / 1e9 / peaks["hbm"])})

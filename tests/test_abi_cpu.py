@@ -57,6 +57,19 @@ def test_workspace_bytes(m):
         ops.make_desc(16, 7168, 2048, 256, 8, out_mode=m.lib.OUT_COMBINED))
 
 
+def test_workspace_bytes_never_shrink_with_tokens(m):
+    """A layer sizes its workspace once for max_tokens and then runs any smaller batch in it."""
+    ops = m.ops
+    for kw in (dict(H=512, I=256, E=64, k=6, I_shared=256), dict(H=4096, I=14336, E=8, k=2)):
+        prev = 0
+        for T in (1, 2, 63, 64, 80, 85, 86, 128, 255, 256, 257, 600, 4096):
+            d = ops.make_desc(T, kw["H"], kw["I"], kw["E"], kw["k"], I_shared=kw.get("I_shared", 0),
+                              out_mode=m.lib.OUT_COMBINED)
+            n = ops.experts_workspace_bytes(d)
+            assert n >= prev, (kw, T, n, prev)
+            prev = n
+
+
 def test_op_surface_matches_reference_names_and_schemas(m):
     m.load_ops()
     want = {

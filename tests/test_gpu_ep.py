@@ -1,0 +1,79 @@
+"""Expert-parallel CUDA path.  With one visible GPU the whole path (pack, all-to-all, unpack, grouped MLP, indexed
+combine) runs on a single-rank NCCL group; with two or more GPUs a 2-rank job is spawned and every rank is checked
+against the oracle over ALL experts."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _run_rank(rank, world, port, q):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    sys.path.insert(0, ROOT)
+    torch.cuda.set_device(rank)
+    dev = f"cuda:{rank}"
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device(dev))
+    try:
+        import torch_tpu_b200  # noqa: F401
+        from torch_tpu_b200.ep import EPFusedMoE
+        from torch_tpu_b200.layer import FusedMoE, MoEConfig
+        H, I, E, k, Is = 512, 256, 16, 4, 256
+        cfg = MoEConfig(H, I, E, k, "sigmoid", 4, 2, True, 2.5, shared_intermediate=Is)
+        bias = torch.randn(E, generator=torch.Generator().manual_seed(3)) * 0.01
+        shared = O.make_expert_weights(1, H, Is, seed=99)
+        full = O.make_expert_weights(E, H, I, seed=5)
+        El = E // world
+        local = tuple(t[rank * El:(rank + 1) * El].contiguous().to(dev) for t in full)
+        T = 150 + 37 * rank
+        x, _, _ = O.make_inputs(T, H, E, seed=10 + rank, router_std=0.2)
+        _, wr, _ = O.make_inputs(1, H, E, seed=1, router_std=0.2)
+        layer = FusedMoE(cfg, wr.to(dev), *local, bias=bias.to(dev), shared=tuple(t.to(dev) for t in shared),
+                         max_tokens=256, alloc_workspace=False)
+        ep = EPFusedMoE(layer, E)
+        y = ep(x.to(dev))
+        torch.cuda.synchronize()
+        ids, w = layer.ids[:T].cpu(), layer.topk_w[:T].cpu()
+        wid, _ = O.route_sigmoid_grouped(layer.logits[:T].cpu(), bias, 4, 2, k, 2.5)
+        want = O.moe_layer_w8a8(x, ids, full, shared=tuple(t[0] for t in shared), topk_w=w)
+        m = O.parity_metrics(y, want)
+        ok_rows = O.tie_free_rows(torch.sigmoid(layer.logits[:T].cpu()) + bias, k, 4, 2)
+        ids_ok = bool(torch.equal(ids[ok_rows], wid[ok_rows]))
+        q.put((rank, ids_ok and m["max_rel"] <= 2e-2 and m["cosine"] >= 0.9995, m["max_rel"], m["cosine"]))
+    except Exception:
+        import traceback
+        q.put((rank, False, "exception", traceback.format_exc()[-1500:]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_ep_cuda_path(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_run_rank, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+    assert all(r[1] for r in res), res

@@ -143,6 +143,10 @@ def test_layer_end_to_end(m, cfgname):
     met = O.parity_metrics(y, want)
     assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
     assert int(layer.status.item()) == 0
+    # CUDA-graph replay gives the same bits
+    yg = layer.forward_graph(x.to(DEV))
+    torch.cuda.synchronize()
+    assert torch.equal(yg, y)
     # host-buffer entry point
     xh, oh = x.pin_memory(), torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()
     layer.forward_host(xh, oh)

@@ -8,8 +8,22 @@ namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+constexpr int64_t kSplitMaxPairs = 512;  // the down GEMM splits K over CTAs only for batches this small
+
+// K splits of the down GEMM: with few (token,slot) pairs there are fewer output tiles than SMs and every tile has a
+// long K loop (K = I), so the weight stream would be pulled by a handful of SMs.
+int choose_ksplit(int64_t P, int64_t E, int64_t H, int64_t I) {
+  if (P > kSplitMaxPairs) return 1;
+  const int64_t tiles = (P < E ? P : E) * ((H + 255) / 256);
+  int64_t ks = (moe_device_sm_count() + tiles - 1) / tiles;
+  const int64_t kb = I / kBlock;
+  if (ks > kb / 4) ks = kb / 4;
+  if (ks > 8) ks = 8;
+  return ks < 1 ? 1 : (int)ks;
+}
+
 struct WsLayout {
-  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32;
+  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32, y32;
   size_t s_offsets, s_mtiles, s_nmt, s_xq, s_xs, s_hq, s_hs, s_y;
   size_t total;
   int64_t P, ld, lds;
@@ -42,6 +56,9 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   L.hq = take(w8a8 ? (size_t)P * d.I : (size_t)P * d.I * 2);
   L.hs = take(w8a8 ? nI * (size_t)L.ld * sizeof(float) : 0);
   L.y = take(d.out_mode == B200MOE_OUT_COMBINED ? (size_t)P * d.H * 2 : 0);
+  // fp32 partial sums of the K-split down GEMM (decode-size batches only)
+  // (sized for min(P, limit) rows whatever P is, so that the workspace size never shrinks when T grows)
+  L.y32 = take(w8a8 ? (size_t)(P < kSplitMaxPairs ? P : kSplitMaxPairs) * d.H * sizeof(float) : 0);
   // fp32 copies of bf16 block scales (the tensor-core kernels read fp32 scales only)
   L.sc32 = take(d.scale_dtype == B200MOE_BF16 && w8a8 ? 3 * (size_t)d.E * nI * nH * sizeof(float) : 0);
   if (d.I_shared > 0) {
@@ -200,7 +217,13 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     if (tc2) {
       MoeGemmArgs t = g2;
       if (cvt) t.s0 = sc32 + 2 * nsc, t.scale_dtype = B200MOE_F32;
+      t.ksplit = choose_ksplit(L.P, d->E, d->H, d->I);
+      if (t.ksplit > 1) {
+        t.out32 = reinterpret_cast<float*>(ws + L.y32);
+        cudaMemsetAsync(t.out32, 0, (size_t)L.P * d->H * sizeof(float), st);
+      }
       rc = moe_gemm2_tc(t, st);
+      if (!rc && t.ksplit > 1) rc = moe_f32_rows_to_bf16(g2.out, t.out32, L.P * d->H, st);
     } else {
       rc = moe_gemm2_simple(g2, d->act_mode, st);
     }
@@ -286,6 +309,110 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     if (rc) return rc;
   }
   return B200MOE_OK;
+}
+
+// ---- grouped MLP on rows that are already quantised and sorted by expert ------------------------------------------
+namespace {
+struct GmLayout {
+  size_t mtiles, nmt, hq, hs, sc32, total;
+  int max_mtiles;
+};
+GmLayout gm_layout(int64_t R, int64_t H, int64_t I, int64_t E, int64_t ld, int scale_dtype) {
+  GmLayout L{};
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = o;
+    o = align_up(o + bytes, 256);
+    return at;
+  };
+  L.max_mtiles = (int)(R / kTileM + E);
+  L.mtiles = take((size_t)L.max_mtiles * 2 * sizeof(int32_t));
+  L.nmt = take(sizeof(int32_t));
+  L.hq = take((size_t)R * I);
+  L.hs = take((size_t)(I / kBlock) * ld * sizeof(float));
+  L.sc32 = take(scale_dtype == B200MOE_BF16 ? 3 * (size_t)E * (I / kBlock) * (H / kBlock) * sizeof(float) : 0);
+  L.total = o;
+  return L;
+}
+}  // namespace
+
+extern "C" size_t b200moe_grouped_mlp_workspace_bytes(int64_t R, int64_t H, int64_t I, int64_t E, int64_t ld,
+                                                      int scale_dtype) {
+  if (R < 0 || H <= 0 || I <= 0 || E <= 0 || H % kBlock || I % kBlock || ld < R) return 0;
+  return gm_layout(R, H, I, E, ld, scale_dtype).total;
+}
+
+extern "C" int b200moe_grouped_mlp(void* y, const uint8_t* xq, const float* xs_t, int64_t ld,
+                                   const int32_t* expert_offsets, const int32_t* row_map, const void* w_gate,
+                                   const void* w_up, const void* w_down, const void* s_gate, const void* s_up,
+                                   const void* s_down, int scale_dtype, int64_t R, int64_t H, int64_t I, int64_t E,
+                                   int impl, void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(R >= 0 && H > 0 && I > 0 && E > 0 && ld >= R);
+  MOE_CHECK_ARG(scale_dtype == B200MOE_F32 || scale_dtype == B200MOE_BF16);
+  MOE_CHECK_ARG(impl >= B200MOE_IMPL_AUTO && impl <= B200MOE_IMPL_TCGEN05);
+  MOE_CHECK_SHAPE(H % kBlock == 0 && I % kBlock == 0 && E <= 1024 && R < (1 << 24) && E * I < (int64_t(1) << 31));
+  if (R == 0) return B200MOE_OK;
+  MOE_CHECK_ARG(y && xq && xs_t && expert_offsets && w_gate && w_up && w_down && s_gate && s_up && s_down);
+  if (!moe_aligned16(y) || !moe_aligned16(xq) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
+      !moe_aligned16(w_down))
+    return B200MOE_EALIGN;
+  const GmLayout L = gm_layout(R, H, I, E, ld, scale_dtype);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return B200MOE_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = reinterpret_cast<char*>(workspace);
+  const bool use_tc = impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
+  if (impl == B200MOE_IMPL_TCGEN05 && !use_tc) return B200MOE_EDRIVER;
+  int32_t* mtiles = reinterpret_cast<int32_t*>(ws + L.mtiles);
+  int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
+  int rc = moe_build_mtiles(mtiles, nmt, expert_offsets, (int)E, st);
+  if (rc) return rc;
+  const void *sg = s_gate, *su = s_up, *sd = s_down;
+  int sdt = scale_dtype;
+  if (use_tc && scale_dtype == B200MOE_BF16) {
+    const int64_t nsc = E * (I / kBlock) * (H / kBlock);
+    float* sc32 = reinterpret_cast<float*>(ws + L.sc32);
+    scales_to_f32_kernel<<<(unsigned)((nsc + 255) / 256), 256, 0, st>>>(
+        sc32, reinterpret_cast<const __nv_bfloat16*>(s_gate), reinterpret_cast<const __nv_bfloat16*>(s_up),
+        reinterpret_cast<const __nv_bfloat16*>(s_down), nsc);
+    rc = moe_launch_status();
+    if (rc) return rc;
+    sg = sc32, su = sc32 + nsc, sd = sc32 + 2 * nsc, sdt = B200MOE_F32;
+  }
+  MoeGemmArgs g{};
+  g.aq = xq;
+  g.as_t = xs_t;
+  g.ld = ld;
+  g.row_map = nullptr;
+  g.div = 1;
+  g.w0 = reinterpret_cast<const uint8_t*>(w_gate);
+  g.w1 = reinterpret_cast<const uint8_t*>(w_up);
+  g.s0 = sg;
+  g.s1 = su;
+  g.scale_dtype = sdt;
+  g.mtiles = mtiles;
+  g.num_mtiles = nmt;
+  g.offsets = expert_offsets;
+  g.max_mtiles = L.max_mtiles;
+  g.P = R;
+  g.H = (int)H;
+  g.I = (int)I;
+  g.E = (int)E;
+  g.hq = reinterpret_cast<uint8_t*>(ws + L.hq);
+  g.hs_t = reinterpret_cast<float*>(ws + L.hs);
+  g.status = status;
+  rc = use_tc ? moe_gemm1_tc(g, st) : moe_gemm1_simple(g, B200MOE_ACT_W8A8, st);
+  if (rc) return rc;
+  MoeGemmArgs g2 = g;
+  g2.aq = g.hq;
+  g2.as_t = g.hs_t;
+  g2.row_map = row_map;
+  g2.w0 = reinterpret_cast<const uint8_t*>(w_down);
+  g2.w1 = nullptr;
+  g2.s0 = sd;
+  g2.s1 = nullptr;
+  g2.out = reinterpret_cast<__nv_bfloat16*>(y);
+  return use_tc ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, B200MOE_ACT_W8A8, st);
 }
 
 extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }

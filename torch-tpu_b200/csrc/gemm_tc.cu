@@ -80,6 +80,8 @@ struct TcArgs {
   const int32_t* offsets;
   const int32_t* row_map;
   int H, I, NT;
+  int KS;        // K splits (down GEMM of decode-size batches); 1 = none
+  float* out32;  // fp32 accumulation target when KS > 1
   uint8_t* hq;
   float* hs_t;
   __nv_bfloat16* out;
@@ -246,8 +248,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const uint32_t tmem_base = sh->tmem_base;
 
   const int num_mtiles = *a.num_mtiles;
-  const int total_tiles = num_mtiles * a.NT;
-  const int KB = (GEMM2 ? a.I : a.H) / kBlock;
+  const int total_tiles = num_mtiles * a.NT * a.KS;  // work items: (n-tile, m-tile, K split)
+  const int KB_all = (GEMM2 ? a.I : a.H) / kBlock;
   const int nH = a.H / kBlock, nI = a.I / kBlock;
 
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
@@ -258,9 +260,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       bool ok = true;
       PROF_DECL(p_wait);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
+        const int ks = t % a.KS, tt = t / a.KS;
+        const int nt = tt / num_mtiles, mt = tt - nt * num_mtiles;
         const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % TC_STAGES;
           const uint32_t ph = (it / TC_STAGES) & 1;
           PROF_T0(tw);
@@ -299,7 +303,9 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       PROF_DECL(m_wtmem);
       PROF_T0(m_t0);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < KB; ++kb, ++it) {
+        const int ks = t % a.KS;
+        const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % TC_STAGES;
           const uint32_t ph = (it / TC_STAGES) & 1;
           const int buf = it & 1;
@@ -353,11 +359,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     PROF_DECL(e_s4);
     PROF_T0(e_t0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const int nt = t / num_mtiles, mt = t - nt * num_mtiles;
+      const int ks = t % a.KS, tt = t / a.KS;
+      const int nt = tt / num_mtiles, mt = tt - nt * num_mtiles;
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
       const int row_end = a.offsets[e + 1];
+      const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
+      const int KB = kb1 - kb0;  // K blocks of this work item
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
+      const bool warp_has_rows = row0 + q * 32 < row_end;  // uniform over the warp
       // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's 64-column span of half j
       uint64_t acc[2][32];
 #pragma unroll
@@ -365,12 +375,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[j][i] = 0ull;
       // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here
-      const float* __restrict__ ws0 = reinterpret_cast<const float*>(a.s0) + (GEMM2 ? (int64_t)e * nI * nH + 2 * nt
+      const float* ws0 = reinterpret_cast<const float*>(a.s0) + (GEMM2 ? (int64_t)e * nI * nH + 2 * nt
                                                                                    : ((int64_t)e * nI + nt) * nH);
-      const float* __restrict__ ws1 = GEMM2 ? ws0 + ((2 * nt + 1 < nH) ? 1 : 0)
+      const float* ws1 = GEMM2 ? ws0 + ((2 * nt + 1 < nH) ? 1 : 0)
                                             : reinterpret_cast<const float*>(a.s1) + ((int64_t)e * nI + nt) * nH;
       const int sstep = GEMM2 ? nH : 1;
-      const float* __restrict__ sap = a.as_t + grow;
+      ws0 += (int64_t)kb0 * sstep;
+      ws1 += (int64_t)kb0 * sstep;
+      const float* __restrict__ sap = a.as_t + (int64_t)kb0 * a.ld + grow;
       // scales are fetched three K blocks ahead (the activation-scale lines come from L2)
       float sa0 = valid ? sap[0] : 0.f, sa1 = (valid && KB > 1) ? sap[a.ld] : 0.f,
             sa2 = (valid && KB > 2) ? sap[2 * a.ld] : 0.f;
@@ -393,6 +405,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         PROF_ADD(e_wait, tw);
         PROF_T0(tl);
         tc_fence_after();
+        if (!warp_has_rows) {  // decode-size batches: most row quarters are empty; just hand the buffer back
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+          continue;
+        }
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hlf * 64;
         const uint64_t f0p = pack2(f0, f0), f1p = pack2(f1, f1);
         uint32_t s0[32], s1[32];
@@ -492,7 +510,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int col = nt * 256 + j * 128 + hlf * 64;
-          if (col < a.H) {
+          if (col < a.H && a.KS > 1) {  // K split: partial sums meet in the fp32 buffer
+            float* dst32 = a.out32 + dstrow * a.H + col;
+#pragma unroll
+            for (int w = 0; w < 32; ++w) {
+              const float2 v = unpack2(acc[j][w]);
+              atomicAdd(dst32 + 2 * w, v.x);
+              atomicAdd(dst32 + 2 * w + 1, v.y);
+            }
+          } else if (col < a.H) {
             uint4* dst = reinterpret_cast<uint4*>(a.out + dstrow * a.H + col);
 #pragma unroll
             for (int v4 = 0; v4 < 8; ++v4) {
@@ -599,6 +625,8 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.H = g.H;
   a.I = g.I;
   a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
+  a.KS = (GEMM2 && g.ksplit > 1 && g.out32) ? g.ksplit : 1;
+  a.out32 = g.out32;
   a.hq = g.hq;
   a.hs_t = g.hs_t;
   a.out = g.out;
@@ -612,7 +640,7 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
     cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
     attr = true;
   }
-  const long long max_tiles = (long long)g.max_mtiles * a.NT;
+  const long long max_tiles = (long long)g.max_mtiles * a.NT * a.KS;
   const int grid = (int)(max_tiles < device_sm_count() ? max_tiles : device_sm_count());
   moe_gemm_tc_kernel<GEMM2><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
   return moe_launch_status();
@@ -635,6 +663,24 @@ bool moe_tc_available() {
   }();
   return ok;
 }
+
+namespace {
+__global__ void f32_rows_to_bf16_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ in, int64_t n) {
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i + 3 < n) {
+    const float4 v = *reinterpret_cast<const float4*>(in + i);
+    *reinterpret_cast<__nv_bfloat162*>(out + i) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(out + i + 2) = __floats2bfloat162_rn(v.z, v.w);
+  }
+}
+}  // namespace
+
+int moe_f32_rows_to_bf16(__nv_bfloat16* out, const float* in, int64_t n, cudaStream_t st) {
+  f32_rows_to_bf16_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, st>>>(out, in, n);
+  return moe_launch_status();
+}
+
+int moe_device_sm_count() { return device_sm_count(); }
 
 int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<false>(a, st); }
 int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<true>(a, st); }

@@ -31,6 +31,8 @@ struct MoeGemmArgs {
   float* hs_t;              // gemm1 W8A8: [I/128, ld]
   __nv_bfloat16* h16;       // gemm1 W8A16: bf16 [P,I]
   __nv_bfloat16* out;       // gemm2: bf16 rows of H, row index = row_map ? row_map[r] : r
+  int ksplit;               // gemm2 (tensor-core path): > 1 splits K over CTAs, partial sums added into out32
+  float* out32;             // fp32 [rows,H], zero on entry, same row indexing as out (needed when ksplit > 1)
   int32_t* status;
 };
 
@@ -42,4 +44,6 @@ int moe_gemm1_simple(const MoeGemmArgs& a, int act_mode, cudaStream_t st);
 int moe_gemm2_simple(const MoeGemmArgs& a, int act_mode, cudaStream_t st);
 int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st);
 int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st);
+int moe_f32_rows_to_bf16(__nv_bfloat16* out, const float* in, int64_t n, cudaStream_t st);
+int moe_device_sm_count();
 bool moe_tc_available();

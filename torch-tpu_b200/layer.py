@@ -31,7 +31,8 @@ class FusedMoE:
     ``[E]`` fp32 (added to the scores for selection only), optional ``logit_bias`` ``[E]`` fp32 (added to the logits), optional shared expert ``(wg,wu,wd,sg,su,sd)`` with a leading dim of 1."""
 
     def __init__(self, cfg: MoEConfig, router_w, wg, wu, wd, sg, su, sd, bias=None, shared: Optional[Tuple] = None,
-                 logit_bias=None, max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO):
+                 logit_bias=None, max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO,
+                 alloc_workspace: bool = True):
         self.cfg = cfg
         self.router_w, self.bias, self.logit_bias = router_w, bias, logit_bias
         self.w = (wg, wu, wd, sg, su, sd)
@@ -47,9 +48,12 @@ class FusedMoE:
         self.out = torch.empty(max_tokens, H, dtype=torch.bfloat16, device=dev)
         self.x_dev = torch.empty(max_tokens, H, dtype=torch.bfloat16, device=dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-        d = ops.make_desc(max_tokens, H, cfg.intermediate, E, k, I_shared=cfg.shared_intermediate,
-                          out_mode=L.OUT_COMBINED, act_mode=act_mode, impl=impl, scale_dtype=sg.dtype)
-        self.workspace = torch.empty(ops.experts_workspace_bytes(d) + 256, dtype=torch.uint8, device=dev)
+        self._graphs = {}
+        self.workspace = None
+        if alloc_workspace:  # an expert-parallel shard runs its experts through other entry points
+            d = ops.make_desc(max_tokens, H, cfg.intermediate, E, k, I_shared=cfg.shared_intermediate,
+                              out_mode=L.OUT_COMBINED, act_mode=act_mode, impl=impl, scale_dtype=sg.dtype)
+            self.workspace = torch.empty(ops.experts_workspace_bytes(d) + 256, dtype=torch.uint8, device=dev)
 
     def route(self, x):
         T = x.shape[0]
@@ -71,6 +75,33 @@ class FusedMoE:
                            impl=self.impl, workspace=self.workspace, status=self.status)
 
     __call__ = forward
+
+    def capture(self, T: int):
+        """Capture forward() for exactly T tokens into a CUDA graph (the call allocates nothing and never touches the
+        host, so the whole layer replays as one launch - what matters at decode sizes, where a dozen small kernels
+        would otherwise cost more in launch gaps than in work).  Use forward_graph() afterwards."""
+        x_static = self.x_dev[:T]
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):           # first calls set function attributes: keep them out of the capture
+                self.forward(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = self.forward(x_static)
+        self._graphs[T] = (g, y)
+        return g
+
+    def forward_graph(self, x):
+        """Replay the graph captured for x.shape[0] tokens (captures it on first use)."""
+        T = x.shape[0]
+        if T not in self._graphs:
+            self.capture(T)
+        g, y = self._graphs[T]
+        self.x_dev[:T].copy_(x, non_blocking=True)
+        g.replay()
+        return y
 
     def forward_host(self, x_host, out_host):
         """End-to-end call with HOST buffers (pinned for asynchronous copies): H2D of x, the layer, D2H of the

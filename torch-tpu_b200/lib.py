@@ -48,6 +48,17 @@ SIGNATURES = {
     "b200moe_experts": (c_int, [c_void_p] * 16 + [POINTER(ExpertsDesc), c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200moe_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64,
                                 c_void_p]),
+    "b200moe_combine_indexed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
+                                        c_int64, c_void_p]),
+    "b200moe_grouped_mlp_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
+    "b200moe_grouped_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p] + [c_void_p] * 6 +
+                            [c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "b200moe_ep_packed_row_bytes": (c_int64, [c_int64]),
+    "b200moe_ep_pack_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                     c_void_p]),
+    "b200moe_ep_unpack_ids": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "b200moe_ep_unpack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "b200moe_invert_permutation": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
 }
 
 _lib = None

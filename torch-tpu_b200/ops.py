@@ -165,3 +165,63 @@ def combine(y, w, add=None, out=None):
     L.check(L.lib().b200moe_combine(_ptr(out), _ptr(y), _ptr(w), _DT[w.dtype], _ptr(add), T, k, H, _stream()),
             "b200moe_combine")
     return out
+
+
+def combine_indexed(y, pos, w, add=None, out=None):
+    """out[t,:] = sum_j w[t,j] * y[pos[t*k+j], :] (+ add[t,:]); y bf16 [R,H], pos int32 [T*k] or None."""
+    _chk(y, "y", torch.bfloat16)
+    T, k = w.shape
+    H = y.shape[-1]
+    if out is None:
+        out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    L.check(L.lib().b200moe_combine_indexed(_ptr(out), _ptr(y), _ptr(pos), _ptr(w), _DT[w.dtype], _ptr(add), T, k, H,
+                                            _stream()), "b200moe_combine_indexed")
+    return out
+
+
+def grouped_mlp_workspace_bytes(R, H, I, E, ld, scale_dtype=torch.float32):
+    return L.lib().b200moe_grouped_mlp_workspace_bytes(R, H, I, E, ld, _DT[scale_dtype])
+
+
+def grouped_mlp(y, xq, xs_t, expert_offsets, wg, wu, wd, sg, su, sd, R, row_map=None, impl=L.IMPL_AUTO,
+                workspace=None, status=None):
+    """Gate/up GEMM + SiLU*up + requantise + down GEMM on rows already quantised and sorted by (local) expert."""
+    E, I, H = wg.shape
+    ld = xs_t.shape[1]
+    need = grouped_mlp_workspace_bytes(R, H, I, E, ld, sg.dtype)
+    if workspace is None:
+        workspace = torch.empty(need + 256, dtype=torch.uint8, device=y.device)
+    base = (workspace.data_ptr() + 255) // 256 * 256
+    avail = workspace.numel() - (base - workspace.data_ptr())
+    L.check(L.lib().b200moe_grouped_mlp(_ptr(y), _ptr(xq), _ptr(xs_t), ld, _ptr(expert_offsets), _ptr(row_map),
+                                        _ptr(wg), _ptr(wu), _ptr(wd), _ptr(sg), _ptr(su), _ptr(sd), _DT[sg.dtype], R, H,
+                                        I, E, impl, ctypes.c_void_p(base), avail, _ptr(status), _stream()),
+            "b200moe_grouped_mlp")
+    return y
+
+
+def ep_packed_row_bytes(H):
+    return L.lib().b200moe_ep_packed_row_bytes(H)
+
+
+def ep_pack_rows(rows, x, sorted_pair, ids, experts_per_rank):
+    T, H = x.shape
+    k = ids.shape[1]
+    L.check(L.lib().b200moe_ep_pack_rows(_ptr(rows), _ptr(x), _ptr(sorted_pair), _ptr(ids), T, k, experts_per_rank, H,
+                                         _stream()), "b200moe_ep_pack_rows")
+    return rows
+
+
+def ep_unpack_ids(eid, rows, R, H):
+    L.check(L.lib().b200moe_ep_unpack_ids(_ptr(eid), _ptr(rows), R, H, _stream()), "b200moe_ep_unpack_ids")
+    return eid
+
+
+def ep_unpack_rows(xq, xs_t, rows, order, R, H):
+    L.check(L.lib().b200moe_ep_unpack_rows(_ptr(xq), _ptr(xs_t), xs_t.shape[1], _ptr(rows), _ptr(order), R, H,
+                                           _stream()), "b200moe_ep_unpack_rows")
+
+
+def invert_permutation(inv, perm, n):
+    L.check(L.lib().b200moe_invert_permutation(_ptr(inv), _ptr(perm), n, _stream()), "b200moe_invert_permutation")
+    return inv
