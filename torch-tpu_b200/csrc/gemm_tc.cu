@@ -47,7 +47,7 @@ constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * 
 // Optional per-role cycle accounting (compile with -DMOE_TC_PROFILE): slot[blockIdx.x*8 + i]
 //   0 producer wait(empty)  1 mma wait(full)  2 mma wait(tmem_empty)  3 mma total
 //   4 epilogue wait(tmem_full)  5 epilogue wake->buffer released  6 epilogue rest (FMAs after release, tile end)
-//   7 epilogue total  8 first two TMEM loads  9 FMAs + two more loads + wait  10 unused  11 fence + release
+//   7 epilogue total  8 first two TMEM chunks  9 FMAs + six more chunks  10 unused  11 fence + release
 #ifdef MOE_TC_PROFILE
 __device__ long long g_tc_prof[256 * 12];
 #define PROF_DECL(v) long long v = 0
@@ -61,7 +61,7 @@ __device__ long long g_tc_prof[256 * 12];
 #define PROF_STORE(i, v)
 #endif
 // Ablation switches for timing experiments (compile with -DMOE_TC_ABLATE, select with env MOE_TC_DBG):
-// bit 0 skip FMAs, bit 1 constant scales, bit 2 skip tile end, bit 3 skip TMEM loads, bit 4 skip the B-operand
+// bit 1 constant scales, bit 2 skip tile end, bit 4 skip the B-operand
 // copies, bit 5 skip the MMAs, bit 6 skip all operand copies
 #if defined(MOE_TC_PROFILE) || defined(MOE_TC_ABLATE)
 #define MOE_TC_DBG_ON 1
@@ -147,31 +147,24 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
       : "memory");
 }
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
-// issue only; the destination registers are valid after tc_ld_wait2 on them
-__device__ __forceinline__ void tc_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+// issue only; the destination registers are valid after tc_ld_wait16x2 on them
+__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
 // wait for every outstanding tcgen05.ld; the two register sets are in/out operands so that no use of them can be
 // scheduled above the wait
-__device__ __forceinline__ void tc_ld_wait2(uint32_t (&a)[32], uint32_t (&b)[32]) {
+__device__ __forceinline__ void tc_ld_wait16x2(uint32_t (&a)[16], uint32_t (&b)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
                  "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
-                 "+r"(a[16]), "+r"(a[17]), "+r"(a[18]), "+r"(a[19]), "+r"(a[20]), "+r"(a[21]), "+r"(a[22]), "+r"(a[23]),
-                 "+r"(a[24]), "+r"(a[25]), "+r"(a[26]), "+r"(a[27]), "+r"(a[28]), "+r"(a[29]), "+r"(a[30]), "+r"(a[31]),
                  "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
-                 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15]),
-                 "+r"(b[16]), "+r"(b[17]), "+r"(b[18]), "+r"(b[19]), "+r"(b[20]), "+r"(b[21]), "+r"(b[22]), "+r"(b[23]),
-                 "+r"(b[24]), "+r"(b[25]), "+r"(b[26]), "+r"(b[27]), "+r"(b[28]), "+r"(b[29]), "+r"(b[30]), "+r"(b[31])
+                 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15])
                :
                : "memory");
 }
@@ -252,7 +245,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int KB_all = (GEMM2 ? a.I : a.H) / kBlock;
   const int nH = a.H / kBlock, nI = a.I / kBlock;
 
-  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
@@ -344,8 +337,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       PROF_STORE(3, m_total);
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue (8 warps, 232 registers each)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ------------------------------------------------------------------ epilogue (8 warps, 216 registers each)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int q = warp & 3, hlf = (warp - 4) >> 2;
     const int rit = q * 32 + lane;  // row inside the tile == TMEM lane
     uint32_t it = 0;
@@ -374,27 +367,26 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int i = 0; i < 32; ++i) acc[j][i] = 0ull;
-      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here
-      const float* ws0 = reinterpret_cast<const float*>(a.s0) + (GEMM2 ? (int64_t)e * nI * nH + 2 * nt
-                                                                                   : ((int64_t)e * nI + nt) * nH);
-      const float* ws1 = GEMM2 ? ws0 + ((2 * nt + 1 < nH) ? 1 : 0)
-                                            : reinterpret_cast<const float*>(a.s1) + ((int64_t)e * nI + nt) * nH;
+      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here.
+      // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
+      // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
+      const float* const S0 = reinterpret_cast<const float*>(a.s0);
+      const float* const S1 = GEMM2 ? S0 : reinterpret_cast<const float*>(a.s1);
       const int sstep = GEMM2 ? nH : 1;
-      ws0 += (int64_t)kb0 * sstep;
-      ws1 += (int64_t)kb0 * sstep;
-      const float* __restrict__ sap = a.as_t + (int64_t)kb0 * a.ld + grow;
-      // scales are fetched three K blocks ahead (the activation-scale lines come from L2)
-      float sa0 = valid ? sap[0] : 0.f, sa1 = (valid && KB > 1) ? sap[a.ld] : 0.f,
-            sa2 = (valid && KB > 2) ? sap[2 * a.ld] : 0.f;
-      float wa0 = ws0[0], wa1 = KB > 1 ? ws0[sstep] : 0.f, wa2 = KB > 2 ? ws0[2 * sstep] : 0.f;
-      float wb0 = ws1[0], wb1 = KB > 1 ? ws1[sstep] : 0.f, wb2 = KB > 2 ? ws1[2 * sstep] : 0.f;
+      const int64_t w0i = (GEMM2 ? (int64_t)e * nI * nH + 2 * nt : ((int64_t)e * nI + nt) * nH) + (int64_t)kb0 * sstep;
+      const int64_t w1i = w0i + (GEMM2 ? ((2 * nt + 1 < nH) ? 1 : 0) : 0);
+      auto load_sa = [&](int kb) { return valid ? a.as_t[(int64_t)(kb0 + kb) * a.ld + grow] : 0.f; };
+      // scales are fetched two K blocks ahead (the activation-scale lines come from L2)
+      float sa0 = load_sa(0), sa1 = KB > 1 ? load_sa(1) : 0.f;
+      float wa0 = S0[w0i], wa1 = KB > 1 ? S0[w0i + sstep] : 0.f;
+      float wb0 = S1[w1i], wb1 = KB > 1 ? S1[w1i + sstep] : 0.f;
       for (int kb = 0; kb < KB; ++kb, ++it) {
         const float f0 = DBG(1) ? 1.f : sa0 * wa0, f1 = DBG(1) ? 1.f : sa0 * wb0;
-        sa0 = sa1, sa1 = sa2, wa0 = wa1, wa1 = wa2, wb0 = wb1, wb1 = wb2;
-        if (kb + 3 < KB && !DBG(1)) {
-          sa2 = valid ? sap[(int64_t)(kb + 3) * a.ld] : 0.f;
-          wa2 = ws0[(kb + 3) * sstep];
-          wb2 = ws1[(kb + 3) * sstep];
+        sa0 = sa1, wa0 = wa1, wb0 = wb1;
+        if (kb + 2 < KB && !DBG(1)) {
+          sa1 = load_sa(kb + 2);
+          wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
+          wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
         }
         const int buf = it & 1;
         PROF_T0(tw);
@@ -413,44 +405,30 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         }
         const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hlf * 64;
         const uint64_t f0p = pack2(f0, f0), f1p = pack2(f1, f1);
-        uint32_t s0[32], s1[32];
-#ifdef MOE_TC_DBG_ON
-        if (DBG(3)) {
+        // The thread's 2 x 64 columns leave TMEM in eight 16-column chunks through two 16-register staging sets:
+        // while one set feeds 8 packed FMAs the other set's load is in flight.  (Two 32-register sets overlap a
+        // little more but push the loop over the register file: spills here are L2 round trips.)
+        uint32_t s0[16], s1[16];
+        auto chunk_addr = [&](int c) { return tbase + (c >> 2) * 128 + (c & 3) * 16; };
+        auto fma_chunk = [&](int c, const uint32_t (&sv)[16]) {
+          const uint64_t fp = (c >> 2) ? f1p : f0p;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) s0[i] = s1[i] = 0;
-        }
-        if (!DBG(3)) {
-#endif
-        tc_ld32_issue(tbase, s0);            // half 0, columns 0..31 of the span
-        tc_ld32_issue(tbase + 32, s1);       // half 0, columns 32..63
-        tc_ld_wait2(s0, s1);
-#ifdef MOE_TC_DBG_ON
-        }
-#endif
+          for (int i = 0; i < 8; ++i)
+            acc[c >> 2][(c & 3) * 8 + i] = ffma2(pack2u(sv[2 * i], sv[2 * i + 1]), fp, acc[c >> 2][(c & 3) * 8 + i]);
+        };
+        tc_ld16_issue(chunk_addr(0), s0);
+        tc_ld16_issue(chunk_addr(1), s1);
+        tc_ld_wait16x2(s0, s1);
         PROF_ADD(e_s1, tl);
         PROF_T0(t2);
-#ifdef MOE_TC_DBG_ON
-        if (!DBG(0))
-#endif
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[0][i] = ffma2(pack2u(s0[2 * i], s0[2 * i + 1]), f0p, acc[0][i]);
-#ifdef MOE_TC_DBG_ON
-        if (!DBG(3))
-#endif
-        tc_ld32_issue(tbase + 128, s0);      // half 1, columns 0..31
-#ifdef MOE_TC_DBG_ON
-        if (!DBG(0))
-#endif
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[0][16 + i] = ffma2(pack2u(s1[2 * i], s1[2 * i + 1]), f0p, acc[0][16 + i]);
-#ifdef MOE_TC_DBG_ON
-        if (!DBG(3)) {
-#endif
-        tc_ld32_issue(tbase + 128 + 32, s1); // half 1, columns 32..63
-        tc_ld_wait2(s0, s1);
-#ifdef MOE_TC_DBG_ON
+        for (int c = 0; c < 6; c += 2) {
+          fma_chunk(c, s0);
+          tc_ld16_issue(chunk_addr(c + 2), s0);
+          fma_chunk(c + 1, s1);
+          tc_ld16_issue(chunk_addr(c + 3), s1);
+          tc_ld_wait16x2(s0, s1);
         }
-#endif
         PROF_ADD(e_s2, t2);
         PROF_T0(t4);
         tc_fence_before();                   // all of this block is in registers: hand the buffer back
@@ -459,16 +437,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         PROF_ADD(e_s4, t4);
         PROF_ADD(e_ld, tl);
         PROF_T0(tp);
-#ifdef MOE_TC_DBG_ON
-        if (!DBG(0)) {
-#endif
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[1][i] = ffma2(pack2u(s0[2 * i], s0[2 * i + 1]), f1p, acc[1][i]);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) acc[1][16 + i] = ffma2(pack2u(s1[2 * i], s1[2 * i + 1]), f1p, acc[1][16 + i]);
-#ifdef MOE_TC_DBG_ON
-        }
-#endif
+        fma_chunk(6, s0);
+        fma_chunk(7, s1);
         PROF_ADD(e_end, tp);
       }
       if (!ok) break;
@@ -476,14 +446,13 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (DBG(2)) continue;
       if (!GEMM2) {
         // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over two warps
-        float h[64];
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < 32; ++i) {  // h overwrites the gate accumulators: no second array of 64 registers
           const float2 g = unpack2(acc[0][i]), u = unpack2(acc[1][i]);
-          h[2 * i] = moe_silu_fast(g.x) * u.x;
-          h[2 * i + 1] = moe_silu_fast(g.y) * u.y;
-          amax = fmaxf(amax, fmaxf(fabsf(h[2 * i]), fabsf(h[2 * i + 1])));
+          const float hx = moe_silu_fast(g.x) * u.x, hy = moe_silu_fast(g.y) * u.y;
+          acc[0][i] = pack2(hx, hy);
+          amax = fmaxf(amax, fmaxf(fabsf(hx), fabsf(hy)));
         }
         sh->amax[hlf][rit] = amax;
         asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -498,8 +467,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-              const int i = v4 * 16 + w * 4;
-              ow[w] = moe_f32x4_to_e4m3x4(h[i] * inv, h[i + 1] * inv, h[i + 2] * inv, h[i + 3] * inv);
+              const float2 p0 = unpack2(acc[0][v4 * 8 + w * 2]), p1 = unpack2(acc[0][v4 * 8 + w * 2 + 1]);
+              ow[w] = moe_f32x4_to_e4m3x4(p0.x * inv, p0.y * inv, p1.x * inv, p1.y * inv);
             }
             dst[v4] = o;
           }
