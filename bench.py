@@ -131,7 +131,7 @@ def make_x(T, H, dev, seed, zipf_bias=None):
     return torch.randn(T, H, generator=g).to(torch.bfloat16)
 
 
-def time_steps(fn, steps, warmup, barrier=None):
+def time_steps(fn, steps, warmup, barrier=None, finish=None):
     import torch
     for _ in range(warmup):
         fn()
@@ -143,6 +143,8 @@ def time_steps(fn, steps, warmup, barrier=None):
     e0.record()
     for _ in range(steps):
         fn()
+    if finish:
+        finish()   # e.g. make the timed stream wait for copies running on side streams
     e1.record()
     torch.cuda.synchronize()
     if barrier:
@@ -291,7 +293,7 @@ def main():
         layer.forward_host(xh[it[0] % 4], oh)
         it[0] += 1
 
-    ms_e2e = time_steps(step_e2e, args.steps, args.warmup, barrier)
+    ms_e2e = time_steps(step_e2e, args.steps, args.warmup, barrier, finish=layer.host_join)
 
     if world > 1:
         import torch.distributed as dist

@@ -149,6 +149,8 @@ def test_layer_end_to_end(m, cfgname):
     assert torch.equal(yg, y)
     # host-buffer entry point
     xh, oh = x.pin_memory(), torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()
-    layer.forward_host(xh, oh)
+    for _ in range(3):   # pipelined: two buffers each way
+        layer.forward_host(xh, oh)
+    layer.host_join()
     torch.cuda.synchronize()
     assert torch.equal(oh, y.cpu())

@@ -120,11 +120,13 @@ class EPFusedMoE:
     __call__ = forward
 
     def forward_host(self, x_host, out_host):
-        xd = self.layer.x_dev[:x_host.shape[0]]
-        xd.copy_(x_host, non_blocking=True)
-        y = self.forward(xd)
-        out_host.copy_(y, non_blocking=True)
-        return out_host
+        """Host-buffer entry point, pipelined like FusedMoE.forward_host."""
+        from .layer import _host_pipeline_call
+        return _host_pipeline_call(self, self.forward, x_host, out_host)
+
+    def host_join(self):
+        from .layer import _host_pipeline_join
+        _host_pipeline_join(self)
 
 
 def build_ep_layer(wl: dict, T: int, dev: str, rank: int, world: int, seed: int = 0):

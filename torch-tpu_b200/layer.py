@@ -104,11 +104,62 @@ class FusedMoE:
         return y
 
     def forward_host(self, x_host, out_host):
-        """End-to-end call with HOST buffers (pinned for asynchronous copies): H2D of x, the layer, D2H of the
-        result, all on the current stream.  Returns out_host (valid after a stream synchronise)."""
-        T = x_host.shape[0]
-        xd = self.x_dev[:T]
-        xd.copy_(x_host, non_blocking=True)
-        y = self.forward(xd)
-        out_host.copy_(y, non_blocking=True)
-        return out_host
+        """End-to-end call with HOST buffers (pinned, so that the copies are asynchronous): H2D of x on a copy stream,
+        the layer on the current stream, D2H of the result on a second copy stream, with two device buffers each way -
+        the copies of neighbouring calls overlap the compute of this one, as a serving loop would run it.  out_host is
+        valid after host_join() + a stream synchronise (or torch.cuda.synchronize())."""
+        return _host_pipeline_call(self, self.forward, x_host, out_host)
+
+    def host_join(self):
+        """Make the current stream wait for every copy that forward_host has enqueued."""
+        _host_pipeline_join(self)
+
+
+def _host_pipeline_state(obj, T, H, dev):
+    st = getattr(obj, "_hp", None)
+    if st is None or st["x"][0].shape[0] < T:
+        cap = max(T, getattr(obj, "max_tokens", T))
+        st = dict(i=0, h2d=torch.cuda.Stream(device=dev), d2h=torch.cuda.Stream(device=dev),
+                  x=[torch.empty(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                  y=[torch.empty(cap, H, dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                  x_free=[torch.cuda.Event() for _ in range(2)], x_ready=[torch.cuda.Event() for _ in range(2)],
+                  y_ready=[torch.cuda.Event() for _ in range(2)], y_free=[torch.cuda.Event() for _ in range(2)])
+        cur = torch.cuda.current_stream(dev)
+        for e in st["x_free"] + st["y_free"]:
+            e.record(cur)
+        obj._hp = st
+    return st
+
+
+def _host_pipeline_call(obj, fwd, x_host, out_host):
+    T, H = x_host.shape
+    dev = obj.device if hasattr(obj, "device") else obj.layer.device
+    st = _host_pipeline_state(obj, T, H, dev)
+    i = st["i"] & 1
+    st["i"] += 1
+    cur = torch.cuda.current_stream(dev)
+    xb, yb = st["x"][i][:T], st["y"][i][:T]
+    st["h2d"].wait_event(st["x_free"][i])            # the compute that read this input buffer two calls ago is done
+    with torch.cuda.stream(st["h2d"]):
+        xb.copy_(x_host, non_blocking=True)
+        st["x_ready"][i].record(st["h2d"])
+    cur.wait_event(st["x_ready"][i])
+    cur.wait_event(st["y_free"][i])                  # the D2H that read this output buffer two calls ago is done
+    y = fwd(xb)
+    yb.copy_(y)                                      # device-to-device into the pipeline's own output buffer
+    st["x_free"][i].record(cur)
+    st["y_ready"][i].record(cur)
+    st["d2h"].wait_event(st["y_ready"][i])
+    with torch.cuda.stream(st["d2h"]):
+        out_host.copy_(yb, non_blocking=True)
+        st["y_free"][i].record(st["d2h"])
+    return out_host
+
+
+def _host_pipeline_join(obj):
+    st = getattr(obj, "_hp", None)
+    if st is not None:
+        dev = obj.device if hasattr(obj, "device") else obj.layer.device
+        cur = torch.cuda.current_stream(dev)
+        for e in st["y_free"]:
+            cur.wait_event(e)
