@@ -247,6 +247,12 @@ def main():
     if args.impl == "reference":
         return run_reference(args, wl)
 
+    # Libraries (NCCL prints its version banner) write to stdout; the contract is ONE JSON line there.  Everything
+    # but that line goes to stderr: fd 1 is pointed at fd 2 and the line is written to the saved descriptor.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
     import torch
     import torch_tpu_b200
     from torch_tpu_b200 import lib as L
@@ -378,7 +384,8 @@ def main():
                                     "sample": f"{args.sample_tokens} tokens through the oracle's expert arithmetic "
                                               f"({secs:.1f} s; activated experts dequantised once each)"}
     if rank == 0:
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()

@@ -114,8 +114,8 @@ def test_op_fused_moe_grouped_topk(m):
     torch.testing.assert_close(w32.cpu(), ww, rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("cfgname", ["mixtral_like", "deepseek_like"])
-def test_layer_end_to_end(m, cfgname):
+@pytest.mark.parametrize("cfgname,T", [("mixtral_like", 80), ("deepseek_like", 80), ("deepseek_like", 24)])
+def test_layer_end_to_end(m, cfgname, T):
     from torch_tpu_b200.layer import FusedMoE, MoEConfig
     if cfgname == "mixtral_like":
         cfg = MoEConfig(512, 256, 8, 2)
@@ -124,7 +124,7 @@ def test_layer_end_to_end(m, cfgname):
         cfg = MoEConfig(512, 256, 64, 6, "sigmoid", 8, 4, True, 2.5, shared_intermediate=256)
         bias = torch.randn(64, generator=torch.Generator().manual_seed(1)) * 0.01
         shared = O.make_expert_weights(1, 512, 256, seed=77)
-    T = 80
+    # T = 24 with a shared expert takes the decode-size route: shared expert on the side stream, K split over CTAs
     p = small_problem(T, cfg.hidden, cfg.intermediate, cfg.num_experts, cfg.top_k, seed=21)
     x, wr, _ = O.make_inputs(T, cfg.hidden, cfg.num_experts, seed=21, router_std=0.2)
     layer = FusedMoE(cfg, wr.to(DEV), *(p[n].to(DEV) for n in ("wg", "wu", "wd", "sg", "su", "sd")),
@@ -146,11 +146,12 @@ def test_layer_end_to_end(m, cfgname):
     # CUDA-graph replay gives the same bits
     yg = layer.forward_graph(x.to(DEV))
     torch.cuda.synchronize()
-    assert torch.equal(yg, y)
+    same = torch.equal if T > 64 else (lambda a, b: bool(((a.float() - b.float()).abs() <= 1e-2 * b.float().abs() + 1e-3).all()))
+    assert same(yg, y)   # split-K partial sums are added in arrival order, so only the unsplit route is bit-stable
     # host-buffer entry point
     xh, oh = x.pin_memory(), torch.empty(T, cfg.hidden, dtype=torch.bfloat16).pin_memory()
     for _ in range(3):   # pipelined: two buffers each way
         layer.forward_host(xh, oh)
     layer.host_join()
     torch.cuda.synchronize()
-    assert torch.equal(oh, y.cpu())
+    assert same(oh, y.cpu())

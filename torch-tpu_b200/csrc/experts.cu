@@ -23,7 +23,7 @@ int choose_ksplit(int64_t P, int64_t E, int64_t H, int64_t I) {
 }
 
 struct WsLayout {
-  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32, y32;
+  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32, y32, s_y32;
   size_t s_offsets, s_mtiles, s_nmt, s_xq, s_xs, s_hq, s_hs, s_y;
   size_t total;
   int64_t P, ld, lds;
@@ -71,6 +71,7 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
     L.s_hq = take(w8a8 ? (size_t)d.T * d.I_shared : (size_t)d.T * d.I_shared * 2);
     L.s_hs = take(w8a8 ? nIs * (size_t)L.lds * sizeof(float) : 0);
     L.s_y = take((size_t)d.T * d.H * 2);
+    L.s_y32 = take(w8a8 ? (size_t)(d.T < kSplitMaxPairs ? d.T : kSplitMaxPairs) * d.H * sizeof(float) : 0);
     L.s_sc32 = take(d.scale_dtype == B200MOE_BF16 && w8a8 ? 3 * nIs * nH * sizeof(float) : 0);
   }
   L.total = o;
@@ -86,6 +87,29 @@ __global__ void scales_to_f32_kernel(float* __restrict__ dst, const __nv_bfloat1
     dst[2 * n + i] = __bfloat162float(c[i]);
   }
 }
+
+// Side stream on which the shared expert of a decode-size batch runs next to the routed experts (neither pass fills
+// the GPU on its own there).  Created once per device on first use; the fork/join is by events, so it can be captured
+// into a CUDA graph together with the caller's stream.
+struct SideStream {
+  cudaStream_t s = nullptr;
+  cudaEvent_t fork = nullptr, join = nullptr;
+};
+SideStream* side_stream() {
+  constexpr int kMaxDevices = 64;
+  static SideStream tab[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  SideStream& t = tab[dev];
+  if (!t.s) {
+    if (cudaStreamCreateWithFlags(&t.s, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess)
+      return nullptr;
+  }
+  return &t;
+}
+constexpr int64_t kSharedOverlapMaxTokens = 64;
 
 int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_ARG(d);
@@ -145,6 +169,17 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   // reserved bit 4 = skip permute/quantise, bit 5 = skip gate-up GEMM, bit 6 = skip down GEMM, bit 7 = skip combine
   const bool do_prep = !(d->reserved & 16), do_g1 = !(d->reserved & 32), do_g2 = !(d->reserved & 64),
              do_comb = !(d->reserved & 128);
+
+  // Decode-size batches with a shared expert: the shared expert runs on a side stream beside the routed experts.
+  // The fork is recorded before any routed work is queued, so both passes start together; they share no workspace
+  // region.  One call per device at a time may use the side stream (calls on one device are expected to be queued
+  // from one host thread).
+  SideStream* side = (d->I_shared > 0 && use_tc && d->T <= kSharedOverlapMaxTokens && d->reserved == 0)
+                         ? side_stream() : nullptr;
+  if (side) {
+    if (cudaEventRecord(side->fork, st) != cudaSuccess || cudaStreamWaitEvent(side->s, side->fork, 0) != cudaSuccess)
+      return (int)cudaGetLastError();
+  }
 
   if (do_prep) {
     rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
@@ -232,20 +267,21 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
 
   const void* add = nullptr;
   if (d->I_shared > 0) {
+    cudaStream_t ss = side ? side->s : st;
     if (do_prep) {
-      rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, st);
+      rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, ss);
       if (rc) return rc;
-      rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, st);
+      rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, ss);
       if (rc) return rc;
     }
     if (w8a8 && do_prep) {
       rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.s_xq), reinterpret_cast<float*>(ws + L.s_xs),
-                              L.lds, x, nullptr, 1, d->T, d->H, stream);
+                              L.lds, x, nullptr, 1, d->T, d->H, (void*)ss);
       if (rc) return rc;
     }
     const int64_t nscs = (d->I_shared / kBlock) * (d->H / kBlock);
     if (cvt && do_prep) {
-      scales_to_f32_kernel<<<(unsigned)((nscs + 255) / 256), 256, 0, st>>>(
+      scales_to_f32_kernel<<<(unsigned)((nscs + 255) / 256), 256, 0, ss>>>(
           reinterpret_cast<float*>(ws + L.s_sc32), reinterpret_cast<const __nv_bfloat16*>(shared_s_gate),
           reinterpret_cast<const __nv_bfloat16*>(shared_s_up), reinterpret_cast<const __nv_bfloat16*>(shared_s_down),
           nscs);
@@ -277,9 +313,9 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
       if (tc1) {
         MoeGemmArgs t = s;
         if (cvt) t.s0 = ssc32, t.s1 = ssc32 + nscs, t.scale_dtype = B200MOE_F32;
-        rc = moe_gemm1_tc(t, st);
+        rc = moe_gemm1_tc(t, ss);
       } else {
-        rc = moe_gemm1_simple(s, d->act_mode, st);
+        rc = moe_gemm1_simple(s, d->act_mode, ss);
       }
     }
     if (rc) return rc;
@@ -296,12 +332,22 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
       if (tc2) {
         MoeGemmArgs t = s2;
         if (cvt) t.s0 = ssc32 + 2 * nscs, t.scale_dtype = B200MOE_F32;
-        rc = moe_gemm2_tc(t, st);
+        t.ksplit = choose_ksplit(d->T, 1, d->H, d->I_shared);
+        if (t.ksplit > 1) {
+          t.out32 = reinterpret_cast<float*>(ws + L.s_y32);
+          cudaMemsetAsync(t.out32, 0, (size_t)d->T * d->H * sizeof(float), ss);
+        }
+        rc = moe_gemm2_tc(t, ss);
+        if (!rc && t.ksplit > 1) rc = moe_f32_rows_to_bf16(s2.out, t.out32, d->T * d->H, ss);
       } else {
-        rc = moe_gemm2_simple(s2, d->act_mode, st);
+        rc = moe_gemm2_simple(s2, d->act_mode, ss);
       }
     }
     if (rc) return rc;
+    if (side) {
+      if (cudaEventRecord(side->join, ss) != cudaSuccess || cudaStreamWaitEvent(st, side->join, 0) != cudaSuccess)
+        return (int)cudaGetLastError();
+    }
     add = ws + L.s_y;
   }
   if (combined && do_comb) {
