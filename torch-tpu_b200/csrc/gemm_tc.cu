@@ -25,13 +25,33 @@
 
 namespace {
 
-constexpr int TC_THREADS = 384;  // three warpgroups: {producer, MMA, 2 idle}, 2 x 4 epilogue warps
+#ifndef MOE_TC_CG
+#define MOE_TC_CG 2
+#endif
+constexpr int TC_CG = MOE_TC_CG;             // epilogue column groups (each 4 warps = the four TMEM lane quarters)
+constexpr int TC_CW = 128 / TC_CG;           // columns of each 128-column half that one epilogue thread owns
+constexpr int TC_CH = 16;                    // columns per tcgen05.ld (= registers of one staging set)
+constexpr int TC_CPH = TC_CW / TC_CH;        // TMEM chunks per half
+constexpr int TC_NC = 2 * TC_CPH;            // chunks per thread and K block
+constexpr int TC_EPI_THREADS = 128 * TC_CG;
+constexpr int TC_THREADS = 128 + TC_EPI_THREADS;  // warpgroup 0 = {producer, MMA, 2 idle}, then the epilogue warps
+// setmaxnreg targets: warpgroup 0 gives registers to the epilogue.  The increase blocks until the CTA's pool (the
+// launch-time count x threads) holds enough, so 128 * LO + TC_EPI_THREADS * HI must not exceed that pool:
+// 384 threads x 168 = 128 x 72 + 256 x 216; 640 threads x 96 = 128 x 32 + 512 x 112.
+#ifndef MOE_TC_REG_HI
+#define MOE_TC_REG_HI (MOE_TC_CG == 2 ? 216 : 112)
+#endif
+constexpr int TC_REG_HI = MOE_TC_REG_HI;
+constexpr int TC_REG_LO = TC_CG == 2 ? (64512 - 256 * TC_REG_HI) / 128 : 32;
+constexpr int TC_REG_LAUNCH = (65536 / TC_THREADS) / 8 * 8;  // what __launch_bounds__(TC_THREADS, 1) lets ptxas use
+static_assert(128 * TC_REG_LO + TC_EPI_THREADS * TC_REG_HI <= TC_THREADS * TC_REG_LAUNCH,
+              "setmaxnreg.inc would wait for registers that the CTA's pool never holds");
 constexpr int TC_STAGES = 4;
 constexpr int TC_A_BYTES = 128 * 128;       // 128 rows x 128 B
 constexpr int TC_B_BYTES = 2 * 128 * 128;   // two 128 x 128 B boxes
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_TMEM_COLS = 512;           // two accumulator buffers of 256 fp32 columns
-constexpr uint32_t TC_SPIN_LIMIT = 4u << 20;  // polls (with back-off) before a wait gives up: ~1 s
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 19;  // polls (each up to MOE_TC_HINT ns, then with back-off) before a wait gives up: ~1 s
 
 struct TcShared {
   uint64_t full[TC_STAGES];
@@ -40,14 +60,14 @@ struct TcShared {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float amax[2][128];
+  float amax[TC_CG][128];
 };
 constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
 
 // Optional per-role cycle accounting (compile with -DMOE_TC_PROFILE): slot[blockIdx.x*8 + i]
 //   0 producer wait(empty)  1 mma wait(full)  2 mma wait(tmem_empty)  3 mma total
 //   4 epilogue wait(tmem_full)  5 epilogue wake->buffer released  6 epilogue rest (FMAs after release, tile end)
-//   7 epilogue total  8 first two TMEM chunks  9 FMAs + six more chunks  10 unused  11 fence + release
+//   7 epilogue total  8 first two TMEM chunks  9 FMAs + six more chunks  10 loop top  11 fence + release
 #ifdef MOE_TC_PROFILE
 __device__ long long g_tc_prof[256 * 12];
 #define PROF_DECL(v) long long v = 0
@@ -101,8 +121,22 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+#ifndef MOE_TC_HINT
+#define MOE_TC_HINT 2000
+#endif
+// One poll.  With a suspend-time hint (ns) the thread sleeps in hardware until the phase completes or the hint runs
+// out, instead of coming back at once: fewer issue slots and shared-memory operations taken from the epilogue warps.
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if MOE_TC_HINT > 0
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"((uint32_t)MOE_TC_HINT)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -110,6 +144,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
+#endif
   return ok;
 }
 // Bounded wait.  Returns false when it gave up or another role already did.
@@ -148,7 +183,7 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint6
 }
 // 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
 // issue only; the destination registers are valid after tc_ld_wait16x2 on them
-__device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+__device__ __forceinline__ void tc_ld_issue(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -159,7 +194,7 @@ __device__ __forceinline__ void tc_ld16_issue(uint32_t taddr, uint32_t (&r)[16])
 }
 // wait for every outstanding tcgen05.ld; the two register sets are in/out operands so that no use of them can be
 // scheduled above the wait
-__device__ __forceinline__ void tc_ld_wait16x2(uint32_t (&a)[16], uint32_t (&b)[16]) {
+__device__ __forceinline__ void tc_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;"
                : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
                  "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
@@ -224,7 +259,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       mbar_init(smem_u32(&sh->empty[s]), 1);
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->tmem_empty[b]), 8);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), 4 * TC_CG);
     }
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -245,7 +280,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int KB_all = (GEMM2 ? a.I : a.H) / kBlock;
   const int nH = a.H / kBlock, nI = a.I / kBlock;
 
-  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REG_LO));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
@@ -288,47 +323,42 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
+    // The loop is flat (the K blocks of all work items of this CTA in one count) and the descriptors are built once:
+    // every instruction of this single thread between two K blocks is latency on the accumulator hand-off.
     if (lane == 0) {
       const uint32_t idesc = make_idesc(GEMM2 ? 1 : 0);
-      uint32_t it = 0;
-      bool ok = true;
+      const uint64_t adesc0 = make_smem_desc(smem_base, 16, 1024);
+      const uint64_t bdesc0 = GEMM2 ? make_smem_desc(smem_base + TC_A_BYTES, 128 * 128, 1024)
+                                    : make_smem_desc(smem_base + TC_A_BYTES, 16, 1024);
+      uint32_t n_it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        const int ks = t % a.KS;
+        n_it += (uint32_t)((int)((int64_t)KB_all * (ks + 1) / a.KS) - (int)((int64_t)KB_all * ks / a.KS));
+      }
       PROF_DECL(m_wfull);
       PROF_DECL(m_wtmem);
       PROF_T0(m_t0);
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const int ks = t % a.KS;
-        const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          const int s = it % TC_STAGES;
-          const uint32_t ph = (it / TC_STAGES) & 1;
-          const int buf = it & 1;
-          const uint32_t bph = (it >> 1) & 1;
-          PROF_T0(tw1);
-          if (!mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag)) {
-            ok = false;
-            break;
-          }
-          PROF_ADD(m_wfull, tw1);
-          PROF_T0(tw2);
-          if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), bph ^ 1, abort_flag)) {
-            ok = false;
-            break;
-          }
-          PROF_ADD(m_wtmem, tw2);
-          tc_fence_after();
-          const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-          const uint64_t adesc = make_smem_desc(sa, 16, 1024);
-          const uint64_t bdesc = GEMM2 ? make_smem_desc(sb, 128 * 128, 1024) : make_smem_desc(sb, 16, 1024);
-          const uint32_t d = tmem_base + buf * 256;
+      for (uint32_t it = 0; it < n_it; ++it) {
+        const uint32_t s = it % TC_STAGES, buf = it & 1;
+        PROF_T0(tw1);
+        if (!mbar_wait(smem_u32(&sh->full[s]), (it / TC_STAGES) & 1, abort_flag)) break;
+        PROF_ADD(m_wfull, tw1);
+        PROF_T0(tw2);
+        if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        PROF_ADD(m_wtmem, tw2);
+        tc_fence_after();
+        // the stage's byte offset, in the descriptors' 16-byte units, stays inside the 14-bit address field
+        const uint64_t adesc = adesc0 + (uint64_t)(s * (TC_STAGE_BYTES >> 4));
+        const uint64_t bdesc = bdesc0 + (uint64_t)(s * (TC_STAGE_BYTES >> 4));
+        const uint32_t d = tmem_base + buf * 256;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            // K advances 32 elements: +32 B inside the swizzle atom (K-major) or +32 rows of 128 B (MN-major)
-            const uint64_t ad = adesc + (uint64_t)(ks * 2);
-            const uint64_t bd = bdesc + (uint64_t)(GEMM2 ? ks * 256 : ks * 2);
-            if (!DBG(5)) tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
-          }
-          tc_commit(smem_u32(&sh->empty[s]));  // wakes the producer (refill) and the epilogue (accumulator ready)
+        for (int ks = 0; ks < 4; ++ks) {
+          // K advances 32 elements: +32 B inside the swizzle atom (K-major) or +32 rows of 128 B (MN-major)
+          const uint64_t ad = adesc + (uint64_t)(ks * 2);
+          const uint64_t bd = bdesc + (uint64_t)(GEMM2 ? ks * 256 : ks * 2);
+          if (!DBG(5)) tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
         }
+        tc_commit(smem_u32(&sh->empty[s]));  // wakes the producer (refill) and the epilogue (accumulator ready)
       }
       PROF_DECL(m_total);
       PROF_ADD(m_total, m_t0);
@@ -337,9 +367,9 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       PROF_STORE(3, m_total);
     }
   } else if (warp >= 4) {
-    // ------------------------------------------------------------------ epilogue (8 warps, 216 registers each)
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-    const int q = warp & 3, hlf = (warp - 4) >> 2;
+    // ------------------------------------------------------------------ epilogue (4 * TC_CG warps)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REG_HI));
+    const int q = warp & 3, cg = (warp - 4) >> 2;
     const int rit = q * 32 + lane;  // row inside the tile == TMEM lane
     uint32_t it = 0;
     bool ok = true;
@@ -361,12 +391,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
       const bool warp_has_rows = row0 + q * 32 < row_end;  // uniform over the warp
-      // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's 64-column span of half j
-      uint64_t acc[2][32];
+      // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's TC_CW-column span of half j
+      uint64_t acc[2][TC_CW / 2];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[j][i] = 0ull;
+        for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = 0ull;
       // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here.
       // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
       // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
@@ -381,6 +411,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       float wa0 = S0[w0i], wa1 = KB > 1 ? S0[w0i + sstep] : 0.f;
       float wb0 = S1[w1i], wb1 = KB > 1 ? S1[w1i + sstep] : 0.f;
       for (int kb = 0; kb < KB; ++kb, ++it) {
+        PROF_T0(ttop);
         const float f0 = DBG(1) ? 1.f : sa0 * wa0, f1 = DBG(1) ? 1.f : sa0 * wb0;
         sa0 = sa1, wa0 = wa1, wb0 = wb1;
         if (kb + 2 < KB && !DBG(1)) {
@@ -389,6 +420,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
         }
         const int buf = it & 1;
+        PROF_ADD(e_s3, ttop);
         PROF_T0(tw);
         if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
           ok = false;
@@ -403,31 +435,32 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
           continue;
         }
-        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + hlf * 64;
+        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + cg * TC_CW;
         const uint64_t f0p = pack2(f0, f0), f1p = pack2(f1, f1);
-        // The thread's 2 x 64 columns leave TMEM in eight 16-column chunks through two 16-register staging sets:
+        // The thread's 2 x TC_CW columns leave TMEM in 16-column chunks through two 16-register staging sets:
         // while one set feeds 8 packed FMAs the other set's load is in flight.  (Two 32-register sets overlap a
         // little more but push the loop over the register file: spills here are L2 round trips.)
-        uint32_t s0[16], s1[16];
-        auto chunk_addr = [&](int c) { return tbase + (c >> 2) * 128 + (c & 3) * 16; };
-        auto fma_chunk = [&](int c, const uint32_t (&sv)[16]) {
-          const uint64_t fp = (c >> 2) ? f1p : f0p;
+        uint32_t s0[TC_CH], s1[TC_CH];
+        auto chunk_addr = [&](int c) { return tbase + (c / TC_CPH) * 128 + (c % TC_CPH) * TC_CH; };
+        auto fma_chunk = [&](int c, const uint32_t (&sv)[TC_CH]) {
+          const uint64_t fp = (c / TC_CPH) ? f1p : f0p;
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            acc[c >> 2][(c & 3) * 8 + i] = ffma2(pack2u(sv[2 * i], sv[2 * i + 1]), fp, acc[c >> 2][(c & 3) * 8 + i]);
+          for (int i = 0; i < TC_CH / 2; ++i)
+            acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i] =
+                ffma2(pack2u(sv[2 * i], sv[2 * i + 1]), fp, acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i]);
         };
-        tc_ld16_issue(chunk_addr(0), s0);
-        tc_ld16_issue(chunk_addr(1), s1);
-        tc_ld_wait16x2(s0, s1);
+        tc_ld_issue(chunk_addr(0), s0);
+        tc_ld_issue(chunk_addr(1), s1);
+        tc_ld_wait(s0, s1);
         PROF_ADD(e_s1, tl);
         PROF_T0(t2);
 #pragma unroll
-        for (int c = 0; c < 6; c += 2) {
+        for (int c = 0; c < TC_NC - 2; c += 2) {
           fma_chunk(c, s0);
-          tc_ld16_issue(chunk_addr(c + 2), s0);
+          tc_ld_issue(chunk_addr(c + 2), s0);
           fma_chunk(c + 1, s1);
-          tc_ld16_issue(chunk_addr(c + 3), s1);
-          tc_ld_wait16x2(s0, s1);
+          tc_ld_issue(chunk_addr(c + 3), s1);
+          tc_ld_wait(s0, s1);
         }
         PROF_ADD(e_s2, t2);
         PROF_T0(t4);
@@ -437,32 +470,34 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         PROF_ADD(e_s4, t4);
         PROF_ADD(e_ld, tl);
         PROF_T0(tp);
-        fma_chunk(6, s0);
-        fma_chunk(7, s1);
+        fma_chunk(TC_NC - 2, s0);
+        fma_chunk(TC_NC - 1, s1);
         PROF_ADD(e_end, tp);
       }
       if (!ok) break;
       PROF_T0(te);
       if (DBG(2)) continue;
       if (!GEMM2) {
-        // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over two warps
+        // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over TC_CG warps
         float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {  // h overwrites the gate accumulators: no second array of 64 registers
+        for (int i = 0; i < TC_CW / 2; ++i) {  // h overwrites the gate accumulators: no second array of 64 registers
           const float2 g = unpack2(acc[0][i]), u = unpack2(acc[1][i]);
           const float hx = moe_silu_fast(g.x) * u.x, hy = moe_silu_fast(g.y) * u.y;
           acc[0][i] = pack2(hx, hy);
           amax = fmaxf(amax, fmaxf(fabsf(hx), fabsf(hy)));
         }
-        sh->amax[hlf][rit] = amax;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        amax = fmaxf(fmaxf(amax, sh->amax[hlf ^ 1][rit]), kAmaxFloor);
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+        sh->amax[cg][rit] = amax;
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
+#pragma unroll
+        for (int o = 0; o < TC_CG; ++o) amax = fmaxf(amax, sh->amax[o][rit]);
+        amax = fmaxf(amax, kAmaxFloor);
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
         const float inv = kFp8Max / amax;
         if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(a.hq + (int64_t)grow * a.I + nt * 128 + hlf * 64);
+          uint4* dst = reinterpret_cast<uint4*>(a.hq + (int64_t)grow * a.I + nt * 128 + cg * TC_CW);
 #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
+          for (int v4 = 0; v4 < TC_CW / 16; ++v4) {
             uint4 o;
             uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
@@ -472,17 +507,17 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
             dst[v4] = o;
           }
-          if (hlf == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
+          if (cg == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
         }
       } else if (valid) {
         const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const int col = nt * 256 + j * 128 + hlf * 64;
+          const int col = nt * 256 + j * 128 + cg * TC_CW;
           if (col < a.H && a.KS > 1) {  // K split: partial sums meet in the fp32 buffer
             float* dst32 = a.out32 + dstrow * a.H + col;
 #pragma unroll
-            for (int w = 0; w < 32; ++w) {
+            for (int w = 0; w < TC_CW / 2; ++w) {
               const float2 v = unpack2(acc[j][w]);
               atomicAdd(dst32 + 2 * w, v.x);
               atomicAdd(dst32 + 2 * w + 1, v.y);
@@ -490,7 +525,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           } else if (col < a.H) {
             uint4* dst = reinterpret_cast<uint4*>(a.out + dstrow * a.H + col);
 #pragma unroll
-            for (int v4 = 0; v4 < 8; ++v4) {
+            for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
               uint4 o;
               __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll

@@ -19,7 +19,7 @@ sys.path.insert(0, ROOT)
 PROF_LIB = os.path.join(HERE, "libb200moe_prof.so")
 NAMES = ["producer wait(empty)", "mma wait(full)", "mma wait(tmem_empty)", "mma total", "epilogue wait(done)",
          "epilogue wake->buffer released", "epilogue rest (FMAs after release, tile end)", "epilogue total",
-         "  first two TMEM loads + wait", "  FMAs + two more loads + wait", "  (unused)", "  fence + release"]
+         "  first two TMEM loads + wait", "  FMAs + two more loads + wait", "  loop top (scale products, next scale loads)", "  fence + release"]
 
 
 def build():
