@@ -69,6 +69,7 @@ def test_grouped_topk_vs_oracle_with_ties(ops, B, E, G, KG, k, dtype):
 @pytest.mark.parametrize("T,H,E,k,mode", [
     (1, 512, 8, 2, "softmax"), (16, 1024, 8, 2, "softmax"), (300, 256, 128, 8, "softmax"),
     (300, 512, 8, 2, "softmax"), (100, 1280, 16, 4, "softmax"), (70, 4096, 5, 2, "softmax"),
+    (3000, 512, 8, 2, "softmax"), (2500, 256, 12, 3, "softmax"),
     (1, 512, 256, 8, "deepseek"), (64, 512, 256, 8, "deepseek"), (1000, 256, 256, 8, "deepseek"),
     (40, 256, 64, 6, "sigmoid_nogroup")])
 def test_route_chain(ops, T, H, E, k, mode):

@@ -378,6 +378,71 @@ router_small_e_kernel(float* __restrict__ logits, const __nv_bfloat16* __restric
     }
 }
 
+// Few experts AND few tokens (decode-size batches): the variant above would run on a handful of blocks.  Here a
+// block owns RS_TOK tokens and its 8 warps split H between them (interleaved 256-column slices, 16-byte loads of x
+// and of the L2-resident router weights); the per-warp partial sums meet in shared memory and are added in warp
+// order, so the result does not depend on timing.
+template <int EP>
+__global__ void __launch_bounds__(RS_WARPS * 32)
+router_small_te_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
+                       const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int E) {
+  __shared__ float part[RS_WARPS][RS_TOK][EP];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t t0 = (int64_t)blockIdx.x * RS_TOK;
+  float acc[RS_TOK][EP];
+#pragma unroll
+  for (int i = 0; i < RS_TOK; ++i)
+#pragma unroll
+    for (int e = 0; e < EP; ++e) acc[i][e] = 0.f;
+  for (int64_t col = (int64_t)(warp * 32 + lane) * 8; col < H; col += RS_WARPS * 256) {
+    float xv[RS_TOK][8];
+#pragma unroll
+    for (int i = 0; i < RS_TOK; ++i) {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (t0 + i < T) raw = *reinterpret_cast<const uint4*>(x + (t0 + i) * H + col);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(b2[j]);
+        xv[i][2 * j] = f.x;
+        xv[i][2 * j + 1] = f.y;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < EP; ++e) {
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (e < E) raw = *reinterpret_cast<const uint4*>(wr + (int64_t)e * H + col);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(b2[j]);
+#pragma unroll
+        for (int i = 0; i < RS_TOK; ++i) {
+          acc[i][e] = fmaf(xv[i][2 * j], f.x, acc[i][e]);
+          acc[i][e] = fmaf(xv[i][2 * j + 1], f.y, acc[i][e]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RS_TOK; ++i)
+#pragma unroll
+    for (int e = 0; e < EP; ++e) {
+      float v = acc[i][e];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) part[warp][i][e] = v;
+    }
+  __syncthreads();
+  if (threadIdx.x < RS_TOK * EP) {
+    const int i = threadIdx.x / EP, e = threadIdx.x % EP;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < RS_WARPS; ++w) v += part[w][i][e];
+    if (t0 + i < T && e < E) logits[(t0 + i) * E + e] = v;
+  }
+}
+
 template <typename F>
 int dispatch_vpt(int64_t n, F&& f) {
   if (n <= 32) return f(std::integral_constant<int, 1>{});
@@ -452,6 +517,10 @@ extern "C" int b200moe_router_logits(float* logits, const void* x, const void* w
   if (T <= 2 * RV_MAXT) {
     dim3 grid((unsigned)((E + 3) / 4), (unsigned)((T + RV_MAXT - 1) / RV_MAXT));
     router_gemv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, E);
+  } else if (E <= 16 && T <= 2048) {
+    const unsigned grid = (unsigned)((T + RS_TOK - 1) / RS_TOK);
+    if (E <= 8) router_small_te_kernel<8><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
+    else router_small_te_kernel<16><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
   } else if (E <= 16) {
     const unsigned grid = (unsigned)((T + RS_WARPS * RS_TOK - 1) / (RS_WARPS * RS_TOK));
     if (E <= 8) router_small_e_kernel<8><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
