@@ -309,82 +309,15 @@ router_gemv_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
   }
 }
 
+constexpr int RS_TOK = 4, RS_WARPS = 8;
 // Few-experts variant (E <= 16, e.g. 8 for Mixtral): the 64x64 tensor-core tile would be mostly padding, and the
-// op is a read of x.  A warp owns 4 tokens and keeps their E partial sums in registers; the router weights are
-// staged in shared memory 1024 columns at a time; x is read once with 16-byte loads.
-constexpr int RS_TOK = 4, RS_WARPS = 8, RS_HC = 1024;
+// op is a read of x.  A block owns RS_TOK tokens and its 8 warps split H between them (interleaved 256-column
+// slices, 16-byte loads of x and of the L2-resident router weights), so that decode-size batches still fill more
+// than a handful of SMs; the per-warp partial sums meet in shared memory and are added in warp order, so the
+// result does not depend on timing.
 template <int EP>
 __global__ void __launch_bounds__(RS_WARPS * 32)
 router_small_e_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
-                      const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int E) {
-  __shared__ __align__(16) __nv_bfloat16 sW[EP * RS_HC];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t0 = ((int64_t)blockIdx.x * RS_WARPS + warp) * RS_TOK;
-  float acc[RS_TOK][EP];
-#pragma unroll
-  for (int i = 0; i < RS_TOK; ++i)
-#pragma unroll
-    for (int e = 0; e < EP; ++e) acc[i][e] = 0.f;
-  for (int64_t h0 = 0; h0 < H; h0 += RS_HC) {
-    const int hc = (int)((H - h0) < RS_HC ? (H - h0) : RS_HC);
-    __syncthreads();
-    for (int c = threadIdx.x * 8; c < EP * RS_HC; c += RS_WARPS * 32 * 8) {
-      const int e = c / RS_HC, col = c % RS_HC;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (e < E && col < hc) v = *reinterpret_cast<const uint4*>(wr + (int64_t)e * H + h0 + col);
-      *reinterpret_cast<uint4*>(sW + c) = v;
-    }
-    __syncthreads();
-    for (int col = lane * 8; col < hc; col += 256) {
-      float xv[RS_TOK][8];
-#pragma unroll
-      for (int i = 0; i < RS_TOK; ++i) {
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (t0 + i < T) raw = *reinterpret_cast<const uint4*>(x + (t0 + i) * H + h0 + col);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __bfloat1622float2(b2[j]);
-          xv[i][2 * j] = f.x;
-          xv[i][2 * j + 1] = f.y;
-        }
-      }
-#pragma unroll
-      for (int e = 0; e < EP; ++e) {
-        uint4 raw = *reinterpret_cast<const uint4*>(sW + e * RS_HC + col);
-        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        float wv[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          float2 f = __bfloat1622float2(b2[j]);
-          wv[2 * j] = f.x;
-          wv[2 * j + 1] = f.y;
-        }
-#pragma unroll
-        for (int i = 0; i < RS_TOK; ++i)
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[i][e] = fmaf(xv[i][j], wv[j], acc[i][e]);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < RS_TOK; ++i)
-#pragma unroll
-    for (int e = 0; e < EP; ++e) {
-      float v = acc[i][e];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0 && t0 + i < T && e < E) logits[(t0 + i) * E + e] = v;
-    }
-}
-
-// Few experts AND few tokens (decode-size batches): the variant above would run on a handful of blocks.  Here a
-// block owns RS_TOK tokens and its 8 warps split H between them (interleaved 256-column slices, 16-byte loads of x
-// and of the L2-resident router weights); the per-warp partial sums meet in shared memory and are added in warp
-// order, so the result does not depend on timing.
-template <int EP>
-__global__ void __launch_bounds__(RS_WARPS * 32)
-router_small_te_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
                        const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int E) {
   __shared__ float part[RS_WARPS][RS_TOK][EP];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -517,12 +450,8 @@ extern "C" int b200moe_router_logits(float* logits, const void* x, const void* w
   if (T <= 2 * RV_MAXT) {
     dim3 grid((unsigned)((E + 3) / 4), (unsigned)((T + RV_MAXT - 1) / RV_MAXT));
     router_gemv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, E);
-  } else if (E <= 16 && T <= 2048) {
-    const unsigned grid = (unsigned)((T + RS_TOK - 1) / RS_TOK);
-    if (E <= 8) router_small_te_kernel<8><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
-    else router_small_te_kernel<16><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
   } else if (E <= 16) {
-    const unsigned grid = (unsigned)((T + RS_WARPS * RS_TOK - 1) / (RS_WARPS * RS_TOK));
+    const unsigned grid = (unsigned)((T + RS_TOK - 1) / RS_TOK);
     if (E <= 8) router_small_e_kernel<8><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
     else router_small_e_kernel<16><<<grid, RS_WARPS * 32, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, (int)E);
   } else {
