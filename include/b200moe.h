@@ -58,7 +58,9 @@ int b200moe_abi_version(void);
 const char* b200moe_error_string(int code);
 
 /* Device-side status word of the last kernels that ran with `status` != NULL: 0 = ok, bit 0 = an
- * expert id outside [0,E) was skipped, bit 1 = a bounded wait inside a kernel gave up. */
+ * expert id outside [0,E) was skipped, bit 1 = a bounded wait inside a kernel gave up, bit 2 = a wait for a
+ * peer rank's flag gave up (peer-memory expert parallelism), bit 3 = a dispatched row did not fit the
+ * destination's capacity and was dropped. */
 
 /* ---- routing -------------------------------------------------------------------------------- */
 
@@ -205,6 +207,49 @@ int b200moe_ep_unpack_rows(uint8_t* xq, float* xs_t, int64_t ld, const uint8_t* 
                            int64_t R, int64_t H, void* stream);
 /* inv[perm[i]] = i */
 int b200moe_invert_permutation(int32_t* inv, const int32_t* perm, int64_t n, void* stream);
+
+/* ---- expert parallelism over peer memory (NVLink) --------------------------------------------------
+ * No reference counterpart (the reference has no expert parallelism).  One process per GPU of one node; every
+ * rank allocates the same set of buffers, exports them (CUDA IPC) and imports its peers' handles, then builds
+ * device arrays of N pointers ("tables", entry r = rank r's buffer, the own entry being the own allocation).
+ * A layer call is: exchange_counts -> plan -> dispatch -> barrier -> grouped_mlp_remote -> barrier -> combine;
+ * all data movement between GPUs is plain peer stores issued by those kernels, and the only waits are flag
+ * barriers with a time limit (status bit 2).  `epoch` must grow by one with every barrier (exchange_counts
+ * contains one) and take the same values on every rank.
+ *
+ * Buffers of one rank, for capacity C rows (C >= the most rows the rank can receive, e.g. N*T*k):
+ *   flags   uint32 [8]            zero at start            cnt    int32 [N][E]
+ *   xq      u8 [C][H]             xs_t   f32 [H/128][ld], ld >= C     src   int32 [C]   (the GEMM operands)
+ *   y       bf16 [T*k][H]         per-slot results of the rank's OWN tokens, written by the expert owners */
+int b200moe_p2p_alloc(void** ptr, size_t bytes);                 /* device allocation, zero-filled */
+int b200moe_p2p_free(void* ptr);
+int b200moe_p2p_export(unsigned char* handle64, void* ptr);      /* 64-byte handle another process can import */
+int b200moe_p2p_import(void** ptr, const unsigned char* handle64);
+int b200moe_p2p_release(void* ptr);                              /* unmap an imported buffer */
+int b200moe_p2p_barrier(const uint64_t* flag_tbl, int64_t N, int64_t rank, uint32_t epoch, int32_t* status,
+                        void* stream);
+/* expert_offsets [E+1] of the rank's own permutation over GLOBAL expert ids -> row `rank` of every peer's cnt;
+ * returns after a barrier, so every rank's cnt is complete for the kernels that follow on the stream */
+int b200moe_ep_exchange_counts(const uint64_t* cnt_tbl, const uint64_t* flag_tbl, const int32_t* expert_offsets,
+                               int64_t E, int64_t N, int64_t rank, uint32_t epoch, int32_t* status, void* stream);
+/* dst_row0 [E]: first row, in the destination's buffers, of this rank's rows of global expert e;
+ * recv_offsets [E/N + 1]: expert_offsets of the rows this rank receives (local experts) */
+int b200moe_ep_plan(int32_t* dst_row0, int32_t* recv_offsets, const int32_t* cnt, int64_t E, int64_t N,
+                    int64_t rank, void* stream);
+/* gather + 1x128 e4m3 quantisation of every (token,slot) row, stored into the owner rank's xq/xs_t/src
+ * (src = rank << 24 | flat pair index t*k+j) */
+int b200moe_ep_dispatch(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_t* src_tbl, const void* x,
+                        const int32_t* sorted_pair, const int32_t* ids, const int32_t* expert_offsets,
+                        const int32_t* dst_row0, int64_t T, int64_t k, int64_t H, int64_t E, int64_t N, int64_t rank,
+                        int64_t ld_remote, int64_t capacity, int32_t* status, void* stream);
+/* b200moe_grouped_mlp on the received rows, each result row stored to out_tbl[src >> 24][(src & 0xFFFFFF), :].
+ * R_capacity bounds the rows (the true count is read from expert_offsets on the device); tensor-core path only;
+ * workspace as b200moe_grouped_mlp_workspace_bytes(R_capacity, ...). */
+int b200moe_grouped_mlp_remote(const uint64_t* out_tbl, const int32_t* row_src, const uint8_t* xq, const float* xs_t,
+                               int64_t ld, const int32_t* expert_offsets, const void* w_gate, const void* w_up,
+                               const void* w_down, const void* s_gate, const void* s_up, const void* s_down,
+                               int scale_dtype, int64_t R_capacity, int64_t H, int64_t I, int64_t E, void* workspace,
+                               size_t workspace_bytes, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,5 +1,6 @@
-"""Expert-parallel CUDA path.  With one visible GPU the whole path (pack, all-to-all, unpack, grouped MLP, indexed
-combine) runs on a single-rank NCCL group; with two or more GPUs a 2-rank job is spawned and every rank is checked
+"""Expert-parallel CUDA paths: the all-to-all one (pack, NCCL all-to-all, unpack, grouped MLP, indexed combine) and
+the peer-memory one (counts exchange, plan, dispatch stores, grouped MLP with peer output, flag barriers).  With one
+visible GPU both run on a single-rank group; with two or more GPUs a 2-rank job is spawned and every rank is checked
 against the oracle over ALL experts."""
 import os
 import socket
@@ -22,7 +23,7 @@ def _free_port():
     return p
 
 
-def _run_rank(rank, world, port, q):
+def _run_rank(rank, world, port, q, mode):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     sys.path.insert(0, ROOT)
@@ -45,9 +46,18 @@ def _run_rank(rank, world, port, q):
         _, wr, _ = O.make_inputs(1, H, E, seed=1, router_std=0.2)
         layer = FusedMoE(cfg, wr.to(dev), *local, bias=bias.to(dev), shared=tuple(t.to(dev) for t in shared),
                          max_tokens=256, alloc_workspace=False)
-        ep = EPFusedMoE(layer, E)
-        y = ep(x.to(dev))
-        torch.cuda.synchronize()
+        if mode == "p2p":
+            from torch_tpu_b200.ep_p2p import P2PFusedMoE
+            ep = P2PFusedMoE(layer, E, max_tokens=256)
+            ep(x[:40].to(dev))             # a first call of another size: epochs and buffers are reused after it
+            y = ep(x.to(dev))
+            torch.cuda.synchronize()
+            assert int(ep.status.item()) == 0, int(ep.status.item())
+            ep.close()
+        else:
+            ep = EPFusedMoE(layer, E)
+            y = ep(x.to(dev))
+            torch.cuda.synchronize()
         ids, w = layer.ids[:T].cpu(), layer.topk_w[:T].cpu()
         wid, _ = O.route_sigmoid_grouped(layer.logits[:T].cpu(), bias, 4, 2, k, 2.5)
         want = O.moe_layer_w8a8(x, ids, full, shared=tuple(t[0] for t in shared), topk_w=w)
@@ -62,15 +72,15 @@ def _run_rank(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [1, 2])
-def test_ep_cuda_path(world):
+@pytest.mark.parametrize("world,mode", [(1, "nccl"), (2, "nccl"), (1, "p2p"), (2, "p2p")])
+def test_ep_cuda_path(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_run_rank, args=(r, world, port, q)) for r in range(world)]
+    procs = [ctx.Process(target=_run_rank, args=(r, world, port, q, mode)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=300) for _ in range(world)]

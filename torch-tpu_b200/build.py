@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 NATIVE_LIB = os.path.join(HERE, "libb200moe.so")
 OPS_LIB = os.path.join(HERE, "libb200_moe_ops.so")
-CU_SOURCES = ["route.cu", "permute.cu", "gemm_simple.cu", "gemm_tc.cu", "experts.cu", "ep.cu"]
+CU_SOURCES = ["route.cu", "permute.cu", "gemm_simple.cu", "gemm_tc.cu", "experts.cu", "ep.cu", "ep_p2p.cu"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

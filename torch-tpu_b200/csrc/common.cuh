@@ -10,6 +10,8 @@
 
 #define B200MOE_STATUS_BAD_EXPERT 1
 #define B200MOE_STATUS_WAIT_TIMEOUT 2
+#define B200MOE_STATUS_PEER_TIMEOUT 4
+#define B200MOE_STATUS_PEER_OVERFLOW 8
 
 constexpr int kBlock = 128;          // quantisation block (columns per activation scale, weight tile edge)
 constexpr float kFp8Max = 448.0f;    // largest finite e4m3 value

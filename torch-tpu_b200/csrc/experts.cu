@@ -388,18 +388,20 @@ extern "C" size_t b200moe_grouped_mlp_workspace_bytes(int64_t R, int64_t H, int6
   return gm_layout(R, H, I, E, ld, scale_dtype).total;
 }
 
-extern "C" int b200moe_grouped_mlp(void* y, const uint8_t* xq, const float* xs_t, int64_t ld,
-                                   const int32_t* expert_offsets, const int32_t* row_map, const void* w_gate,
-                                   const void* w_up, const void* w_down, const void* s_gate, const void* s_up,
-                                   const void* s_down, int scale_dtype, int64_t R, int64_t H, int64_t I, int64_t E,
-                                   int impl, void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+namespace {
+// shared body of b200moe_grouped_mlp (y/row_map) and b200moe_grouped_mlp_remote (row_src/out_tbl)
+int grouped_mlp_impl(void* y, const uint8_t* xq, const float* xs_t, int64_t ld, const int32_t* expert_offsets,
+                     const int32_t* row_map, const int32_t* row_src, const uint64_t* out_tbl, const void* w_gate,
+                     const void* w_up, const void* w_down, const void* s_gate, const void* s_up, const void* s_down,
+                     int scale_dtype, int64_t R, int64_t H, int64_t I, int64_t E, int impl, void* workspace,
+                     size_t workspace_bytes, int32_t* status, void* stream) {
   MOE_CHECK_ARG(R >= 0 && H > 0 && I > 0 && E > 0 && ld >= R);
   MOE_CHECK_ARG(scale_dtype == B200MOE_F32 || scale_dtype == B200MOE_BF16);
   MOE_CHECK_ARG(impl >= B200MOE_IMPL_AUTO && impl <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_SHAPE(H % kBlock == 0 && I % kBlock == 0 && E <= 1024 && R < (1 << 24) && E * I < (int64_t(1) << 31));
   if (R == 0) return B200MOE_OK;
-  MOE_CHECK_ARG(y && xq && xs_t && expert_offsets && w_gate && w_up && w_down && s_gate && s_up && s_down);
-  if (!moe_aligned16(y) || !moe_aligned16(xq) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
+  MOE_CHECK_ARG((y || row_src) && xq && xs_t && expert_offsets && w_gate && w_up && w_down && s_gate && s_up && s_down);
+  if ((y && !moe_aligned16(y)) || !moe_aligned16(xq) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
       !moe_aligned16(w_down))
     return B200MOE_EALIGN;
   const GmLayout L = gm_layout(R, H, I, E, ld, scale_dtype);
@@ -409,6 +411,7 @@ extern "C" int b200moe_grouped_mlp(void* y, const uint8_t* xq, const float* xs_t
   char* ws = reinterpret_cast<char*>(workspace);
   const bool use_tc = impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
   if (impl == B200MOE_IMPL_TCGEN05 && !use_tc) return B200MOE_EDRIVER;
+  if (row_src && !use_tc) return B200MOE_EDRIVER;  // peer output exists on the tensor-core path only
   int32_t* mtiles = reinterpret_cast<int32_t*>(ws + L.mtiles);
   int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
   int rc = moe_build_mtiles(mtiles, nmt, expert_offsets, (int)E, st);
@@ -453,12 +456,37 @@ extern "C" int b200moe_grouped_mlp(void* y, const uint8_t* xq, const float* xs_t
   g2.aq = g.hq;
   g2.as_t = g.hs_t;
   g2.row_map = row_map;
+  g2.row_src = row_src;
+  g2.out_tbl = out_tbl;
   g2.w0 = reinterpret_cast<const uint8_t*>(w_down);
   g2.w1 = nullptr;
   g2.s0 = sd;
   g2.s1 = nullptr;
   g2.out = reinterpret_cast<__nv_bfloat16*>(y);
   return use_tc ? moe_gemm2_tc(g2, st) : moe_gemm2_simple(g2, B200MOE_ACT_W8A8, st);
+}
+}  // namespace
+
+extern "C" int b200moe_grouped_mlp(void* y, const uint8_t* xq, const float* xs_t, int64_t ld,
+                                   const int32_t* expert_offsets, const int32_t* row_map, const void* w_gate,
+                                   const void* w_up, const void* w_down, const void* s_gate, const void* s_up,
+                                   const void* s_down, int scale_dtype, int64_t R, int64_t H, int64_t I, int64_t E,
+                                   int impl, void* workspace, size_t workspace_bytes, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(y);
+  return grouped_mlp_impl(y, xq, xs_t, ld, expert_offsets, row_map, nullptr, nullptr, w_gate, w_up, w_down, s_gate,
+                          s_up, s_down, scale_dtype, R, H, I, E, impl, workspace, workspace_bytes, status, stream);
+}
+
+extern "C" int b200moe_grouped_mlp_remote(const uint64_t* out_tbl, const int32_t* row_src, const uint8_t* xq,
+                                          const float* xs_t, int64_t ld, const int32_t* expert_offsets,
+                                          const void* w_gate, const void* w_up, const void* w_down,
+                                          const void* s_gate, const void* s_up, const void* s_down, int scale_dtype,
+                                          int64_t R_capacity, int64_t H, int64_t I, int64_t E, void* workspace,
+                                          size_t workspace_bytes, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(out_tbl && row_src);
+  return grouped_mlp_impl(nullptr, xq, xs_t, ld, expert_offsets, nullptr, row_src, out_tbl, w_gate, w_up, w_down,
+                          s_gate, s_up, s_down, scale_dtype, R_capacity, H, I, E, B200MOE_IMPL_TCGEN05, workspace,
+                          workspace_bytes, status, stream);
 }
 
 extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }

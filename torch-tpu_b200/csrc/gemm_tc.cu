@@ -99,6 +99,8 @@ struct TcArgs {
   const int32_t* num_mtiles;
   const int32_t* offsets;
   const int32_t* row_map;
+  const int32_t* row_src;   // down GEMM over peer memory: origin tag (rank << 24 | row) of every row ...
+  const uint64_t* out_tbl;  // ... and the per-rank output buffers (device array of pointers)
   int H, I, NT;
   int KS;        // K splits (down GEMM of decode-size batches); 1 = none
   float* out32;  // fp32 accumulation target when KS > 1
@@ -510,7 +512,13 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (cg == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
         }
       } else if (valid) {
-        const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
+        int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
+        __nv_bfloat16* obase = a.out;
+        if (a.row_src) {  // the row's origin rank receives it directly (plain peer stores)
+          const int tag = a.row_src[grow];
+          obase = reinterpret_cast<__nv_bfloat16*>(a.out_tbl[tag >> 24]);
+          dstrow = tag & 0xFFFFFF;
+        }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int col = nt * 256 + j * 128 + cg * TC_CW;
@@ -523,7 +531,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
               atomicAdd(dst32 + 2 * w + 1, v.y);
             }
           } else if (col < a.H) {
-            uint4* dst = reinterpret_cast<uint4*>(a.out + dstrow * a.H + col);
+            uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * a.H + col);
 #pragma unroll
             for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
               uint4 o;
@@ -626,10 +634,12 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.num_mtiles = g.num_mtiles;
   a.offsets = g.offsets;
   a.row_map = g.row_map;
+  a.row_src = GEMM2 ? g.row_src : nullptr;
+  a.out_tbl = g.out_tbl;
   a.H = g.H;
   a.I = g.I;
   a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
-  a.KS = (GEMM2 && g.ksplit > 1 && g.out32) ? g.ksplit : 1;
+  a.KS = (GEMM2 && g.ksplit > 1 && g.out32 && !g.row_src) ? g.ksplit : 1;
   a.out32 = g.out32;
   a.hq = g.hq;
   a.hs_t = g.hs_t;

@@ -1,0 +1,173 @@
+"""Expert parallelism over peer memory: the dispatch and combine exchanges are stores issued by the producing
+kernels themselves (quantise-and-scatter into the owner's GEMM operand buffers; the down GEMM's epilogue into the
+origin's per-slot buffer), with three flag barriers per call and no library collective or host synchronisation on
+the data path.  See torch-tpu_b200/csrc/ep_p2p.cu for the kernels and include/b200moe.h for the C ABI.
+
+``torch.distributed`` is used once, at construction, to exchange the 64-byte memory handles.  The reference has no
+expert-parallel path (torch_tpu/csrc/distributed/c10d/ProcessGroupSCCL.cpp:714-743 is an equal-split all-to-all).
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import lib as L
+from . import ops
+
+
+def _round_up(n, m):
+    return (n + m - 1) // m * m
+
+
+class _RawCuda:
+    """Lets torch view a raw device range (``__cuda_array_interface__``) without copying."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerArena:
+    """One zero-filled device allocation per rank, mapped into every rank of ``group`` (same node), carved into
+    named regions.  ``table(name)`` is a device int64 array: entry r = address of rank r's region."""
+
+    def __init__(self, regions, device, group=None):
+        self.group, self.device = group, torch.device(device)
+        self.N, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.offsets, off = {}, 0
+        for name, nbytes in regions:
+            self.offsets[name] = (off, nbytes)
+            off = _round_up(off + nbytes, 256)
+        self.nbytes = max(off, 256)
+        lib = L.lib()
+        p = ctypes.c_void_p()
+        L.check(lib.b200moe_p2p_alloc(ctypes.byref(p), self.nbytes), "b200moe_p2p_alloc")
+        self.base = p.value
+        h = ctypes.create_string_buffer(64)
+        L.check(lib.b200moe_p2p_export(h, ctypes.c_void_p(self.base)), "b200moe_p2p_export")
+        handles = [None] * self.N
+        dist.all_gather_object(handles, bytes(h.raw), group=group)
+        self.peer_base, self._imported = [], []
+        for r, hb in enumerate(handles):
+            if r == self.rank:
+                self.peer_base.append(self.base)
+                continue
+            q = ctypes.c_void_p()
+            L.check(lib.b200moe_p2p_import(ctypes.byref(q), hb), "b200moe_p2p_import")
+            self.peer_base.append(q.value)
+            self._imported.append(q.value)
+        self._whole = torch.as_tensor(_RawCuda(self.base, self.nbytes), device=self.device)
+        self._tables = {name: torch.tensor([b + o for b in self.peer_base], dtype=torch.int64, device=self.device)
+                        for name, (o, _) in self.offsets.items()}
+        dist.barrier(group=group)   # nobody stores into a peer before every mapping exists
+
+    def table(self, name):
+        return self._tables[name]
+
+    def local(self, name, dtype, shape):
+        o, n = self.offsets[name]
+        return self._whole[o:o + n].view(dtype).view(*shape)
+
+    def close(self):
+        """Unmap the peers' memory, wait until every rank has done so, free the own allocation."""
+        if self.base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        lib = L.lib()
+        for q in self._imported:
+            lib.b200moe_p2p_release(ctypes.c_void_p(q))
+        self._imported = []
+        dist.barrier(group=self.group)
+        self._whole = None
+        lib.b200moe_p2p_free(ctypes.c_void_p(self.base))
+        self.base = None
+
+
+class P2PFusedMoE:
+    """Expert-parallel MoE layer over peer memory.  ``layer`` is a FusedMoE holding the replicated router and the
+    LOCAL expert shard (rank r owns experts [r*E/N, (r+1)*E/N)); every rank may pass up to ``max_tokens`` tokens per
+    call.  Capacity is the worst case (every row of every rank routed to one rank), so no row is ever dropped."""
+
+    def __init__(self, layer, num_experts_global: int, max_tokens: int, group=None):
+        self.layer, self.E, self.group = layer, num_experts_global, group
+        self.N, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.N > 8:
+            raise ValueError("peer-memory expert parallelism spans one node: at most 8 ranks")
+        if num_experts_global % self.N:
+            raise ValueError("the number of experts must be divisible by the number of ranks")
+        self.El = num_experts_global // self.N
+        cfg = layer.cfg
+        self.H, self.k, self.max_tokens = cfg.hidden, cfg.top_k, max_tokens
+        self.dev = torch.device(layer.device)
+        self.cap = self.N * max_tokens * self.k
+        self.ld = _round_up(self.cap, 128)
+        nH = self.H // 128
+        self.arena = PeerArena([("flags", 256), ("cnt", self.N * self.E * 4), ("xq", self.cap * self.H),
+                                ("xs", nH * self.ld * 4), ("src", self.cap * 4),
+                                ("y", max_tokens * self.k * self.H * 2)], self.dev, group)
+        a = self.arena
+        self.cnt = a.local("cnt", torch.int32, (self.N, self.E))
+        self.xq = a.local("xq", torch.uint8, (self.cap, self.H))
+        self.xs = a.local("xs", torch.float32, (nH, self.ld))
+        self.src = a.local("src", torch.int32, (self.cap,))
+        self.y = a.local("y", torch.bfloat16, (max_tokens, self.k, self.H))
+        self.dst_row0 = torch.empty(self.E, dtype=torch.int32, device=self.dev)
+        self.recv_offsets = torch.empty(self.El + 1, dtype=torch.int32, device=self.dev)
+        wg, sg = layer.w[0], layer.w[3]
+        self.I = wg.shape[1]
+        need = ops.grouped_mlp_workspace_bytes(self.cap, self.H, self.I, self.El, self.ld, sg.dtype)
+        self.workspace = torch.empty(need + 256, dtype=torch.uint8, device=self.dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self.epoch = 0
+
+    def _next_epoch(self):
+        self.epoch = (self.epoch + 1) & 0xFFFFFFFF
+        return ctypes.c_uint32(self.epoch)
+
+    def forward(self, x):
+        layer, a, lib = self.layer, self.arena, L.lib()
+        T, H = x.shape
+        if T > self.max_tokens or H != self.H:
+            raise ValueError("x must be [T <= max_tokens, hidden]")
+        N, rank, E = self.N, self.rank, self.E
+        p, st = ops._ptr, ops._stream
+        ids, w = layer.route(x)                                    # ids over GLOBAL experts
+        sorted_pair, offsets = ops.permute(ids, E, status=self.status)
+        L.check(lib.b200moe_ep_exchange_counts(p(a.table("cnt")), p(a.table("flags")), p(offsets), E, N, rank,
+                                               self._next_epoch(), p(self.status), st()), "b200moe_ep_exchange_counts")
+        L.check(lib.b200moe_ep_plan(p(self.dst_row0), p(self.recv_offsets), p(self.cnt), E, N, rank, st()),
+                "b200moe_ep_plan")
+        L.check(lib.b200moe_ep_dispatch(p(a.table("xq")), p(a.table("xs")), p(a.table("src")), p(x), p(sorted_pair),
+                                        p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank, self.ld,
+                                        self.cap, p(self.status), st()), "b200moe_ep_dispatch")
+        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
+                "b200moe_p2p_barrier")
+        wg, wu, wd, sg, su, sd = layer.w
+        base = (self.workspace.data_ptr() + 255) // 256 * 256
+        avail = self.workspace.numel() - (base - self.workspace.data_ptr())
+        L.check(lib.b200moe_grouped_mlp_remote(p(a.table("y")), p(self.src), p(self.xq), p(self.xs), self.ld,
+                                               p(self.recv_offsets), p(wg), p(wu), p(wd), p(sg), p(su), p(sd),
+                                               ops._DT[sg.dtype], self.cap, H, self.I, self.El,
+                                               ctypes.c_void_p(base), avail, p(self.status), st()),
+                "b200moe_grouped_mlp_remote")
+        add = None
+        if layer.shared is not None:                               # local work between the two barriers
+            out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
+            ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
+            add = out1.view(T, H)
+        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
+                "b200moe_p2p_barrier")
+        return ops.combine(self.y[:T], w, add=add)
+
+    __call__ = forward
+
+    def forward_host(self, x_host, out_host):
+        """Host-buffer entry point, pipelined like FusedMoE.forward_host."""
+        from .layer import _host_pipeline_call
+        return _host_pipeline_call(self, self.forward, x_host, out_host)
+
+    def host_join(self):
+        from .layer import _host_pipeline_join
+        _host_pipeline_join(self)
+
+    def close(self):
+        self.arena.close()

@@ -5,7 +5,7 @@ There is no fallback: if ``libb200moe.so`` has not been built, importing the bin
 """
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
@@ -16,7 +16,7 @@ SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
 OUT_PER_SLOT, OUT_COMBINED = 0, 1
 ACT_W8A8, ACT_W8A16 = 0, 1
 IMPL_AUTO, IMPL_SIMPLE, IMPL_TCGEN05 = 0, 1, 2
-STATUS_BAD_EXPERT, STATUS_WAIT_TIMEOUT = 1, 2
+STATUS_BAD_EXPERT, STATUS_WAIT_TIMEOUT, STATUS_PEER_TIMEOUT, STATUS_PEER_OVERFLOW = 1, 2, 4, 8
 
 
 class ExpertsDesc(Structure):
@@ -59,6 +59,18 @@ SIGNATURES = {
     "b200moe_ep_unpack_ids": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200moe_ep_unpack_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200moe_invert_permutation": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "b200moe_p2p_alloc": (c_int, [POINTER(c_void_p), c_size_t]),
+    "b200moe_p2p_free": (c_int, [c_void_p]),
+    "b200moe_p2p_export": (c_int, [c_char_p, c_void_p]),
+    "b200moe_p2p_import": (c_int, [POINTER(c_void_p), c_char_p]),
+    "b200moe_p2p_release": (c_int, [c_void_p]),
+    "b200moe_p2p_barrier": (c_int, [c_void_p, c_int64, c_int64, c_uint32, c_void_p, c_void_p]),
+    "b200moe_ep_exchange_counts": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_uint32, c_void_p,
+                                           c_void_p]),
+    "b200moe_ep_plan": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "b200moe_ep_dispatch": (c_int, [c_void_p] * 8 + [c_int64] * 8 + [c_void_p, c_void_p]),
+    "b200moe_grouped_mlp_remote": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                                                             c_size_t, c_void_p, c_void_p]),
 }
 
 _lib = None
