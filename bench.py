@@ -152,8 +152,14 @@ def time_steps(fn, steps, warmup, barrier=None, finish=None):
     return e0.elapsed_time(e1) / steps  # ms per step
 
 
-def launches_per_step(wl, T, world=1):
+def launches_per_step(wl, T, world=1, ep="nccl"):
     P = T * wl["k"]
+    if world > 1 and ep == "p2p":
+        # router, route, permute | counts exchange, plan, dispatch, barrier | tiles, 2 GEMMs, barrier | combine
+        n = 2 + (1 if P <= 1024 else 3) + 4 + 4 + 1
+        if wl.get("shared"):
+            n += (1 if T <= 1024 else 3) + 1 + 1 + 2
+        return n
     if world > 1:
         # router, route, permute, pack | unpack ids, permute (received rows), unpack rows, tiles, 2 GEMMs | invert, combine
         n = 2 + (1 if P <= 1024 else 3) + 1 + 1 + 3 + 1 + 1 + 2 + 2
@@ -239,6 +245,8 @@ def main():
     ap.add_argument("--workload", default="mixtral", choices=list(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=None, help="tokens per GPU (default: the workload's headline size)")
     ap.add_argument("--sample-tokens", type=int, default=32, help="tokens of the CPU sample")
+    ap.add_argument("--ep", default="p2p", choices=["p2p", "nccl"],
+                    help="exchange of the expert-parallel runs (N > 1): peer-memory stores or NCCL all-to-all")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -274,7 +282,7 @@ def main():
 
     if world > 1:
         from torch_tpu_b200.ep import build_ep_layer
-        layer = build_ep_layer(wl, T, dev, rank, world, seed=0)
+        layer = build_ep_layer(wl, T, dev, rank, world, seed=0, transport=args.ep)
     else:
         layer = build_layer(wl, T_max, dev, seed=0)
 
@@ -290,6 +298,8 @@ def main():
         ms = time_steps(step, args.steps, args.warmup, barrier)
     clocks = cs.summary()
     status = int((layer.layer if world > 1 else layer).status.item())
+    if world > 1 and args.ep == "p2p":
+        status |= int(layer.status.item())
 
     # ---- end to end with host buffers ---------------------------------------------------------------------------
     xh = [x.cpu().pin_memory() for x in xs]
@@ -312,11 +322,11 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: {wl['desc']}, {T} tokens/GPU", "H": wl["H"], "I": wl["I"],
-                       "E": wl["E"], "top_k": wl["k"], "parallelism": f"ep{world}" if world > 1 else "single",
+                       "E": wl["E"], "top_k": wl["k"], "parallelism": f"ep{world} ({args.ep})" if world > 1 else "single",
                        "l2": "weights >> 126 MB L2, 4 rotating input batches"},
             "e2e": {"value": T * world / (ms_e2e / 1000), "unit": "tokens/s", "h2d_bytes_per_step": T * wl["H"] * 2,
                     "d2h_bytes_per_step": T * wl["H"] * 2},
-            "gpu_launches": launches_per_step(wl, T, world) * args.steps, "clocks": clocks, "device_status": status}
+            "gpu_launches": launches_per_step(wl, T, world, args.ep) * args.steps, "clocks": clocks, "device_status": status}
 
     if rank == 0 and world == 1:
         # ---- roofline of the dominant kernel: gate/up GEMM alone on the filled workspace ---------------------------
@@ -388,6 +398,8 @@ def main():
         os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         import torch.distributed as dist
+        if hasattr(layer, "close"):
+            layer.close()
         dist.destroy_process_group()
 
 

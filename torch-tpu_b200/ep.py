@@ -129,9 +129,10 @@ class EPFusedMoE:
         _host_pipeline_join(self)
 
 
-def build_ep_layer(wl: dict, T: int, dev: str, rank: int, world: int, seed: int = 0):
+def build_ep_layer(wl: dict, T: int, dev: str, rank: int, world: int, seed: int = 0, transport: str = "nccl"):
     """Benchmark helper: the rank's shard of a synthetic layer of workload ``wl`` (see bench.py).  Expert weights are
-    seeded per (seed, first local expert), the replicated router/bias/shared expert by ``seed`` alone."""
+    seeded per (seed, first local expert), the replicated router/bias/shared expert by ``seed`` alone.
+    ``transport``: "nccl" (all_to_all_single) or "p2p" (peer-memory stores, ep_p2p.P2PFusedMoE)."""
     import torch
     from . import weights as W
     from .layer import FusedMoE, MoEConfig
@@ -150,4 +151,7 @@ def build_ep_layer(wl: dict, T: int, dev: str, rank: int, world: int, seed: int 
     cfg = MoEConfig(wl["H"], wl["I"], E, wl["k"], wl["score"], wl.get("groups", 1), wl.get("topk_groups", 1), True,
                     wl.get("scale", 1.0), wl.get("shared", 0))
     layer = FusedMoE(cfg, wr, *w, bias=bias, shared=shared, logit_bias=logit_bias, max_tokens=T, alloc_workspace=False)
+    if transport == "p2p":
+        from .ep_p2p import P2PFusedMoE
+        return P2PFusedMoE(layer, E, max_tokens=T)
     return EPFusedMoE(layer, E)
