@@ -61,8 +61,10 @@ struct TcShared {
   uint32_t tmem_base;
   int abort_flag;
   float amax[TC_CG][128];
+  alignas(16) uint8_t ostage[128 * 256];  // down GEMM with peer output: one 128 x 128 bf16 half tile on its way to row-wise stores
 };
 constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
+static_assert(TC_SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
 
 // Optional per-role cycle accounting (compile with -DMOE_TC_PROFILE): slot[blockIdx.x*8 + i]
 //   0 producer wait(empty)  1 mma wait(full)  2 mma wait(tmem_empty)  3 mma total
@@ -511,14 +513,45 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           if (cg == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
         }
-      } else if (valid) {
-        int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
-        __nv_bfloat16* obase = a.out;
-        if (a.row_src) {  // the row's origin rank receives it directly (plain peer stores)
-          const int tag = a.row_src[grow];
-          obase = reinterpret_cast<__nv_bfloat16*>(a.out_tbl[tag >> 24]);
-          dstrow = tag & 0xFFFFFF;
+      } else if (a.row_src) {
+        // Peer output: every row goes to its origin rank (plain peer stores).  A thread owns one row, so storing
+        // from registers would put 16 bytes per lane on the link, 32 rows apart; instead each 128-column half of the
+        // tile is turned through shared memory (16-byte chunks, XOR-swizzled by row so that neither side has bank
+        // conflicts) and a warp stores one row's 256 contiguous bytes per instruction.
+        const int wepi = warp - 4;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col0 = nt * 256 + j * 128;
+          if (col0 >= a.H) break;  // uniform
+          uint4* st16 = reinterpret_cast<uint4*>(sh->ostage);
+#pragma unroll
+          for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const float2 v = unpack2(acc[j][v4 * 4 + w]);
+              o2[w] = __floats2bfloat162_rn(v.x, v.y);
+            }
+            const int chunk = cg * (TC_CW / 8) + v4;
+            st16[rit * 16 + (chunk ^ (rit & 15))] = o;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
+          const uint2* st8 = reinterpret_cast<const uint2*>(sh->ostage);
+          constexpr int ROWS_PER_WARP = 128 / (4 * TC_CG);
+          for (int rr = 0; rr < ROWS_PER_WARP; ++rr) {
+            const int r = wepi * ROWS_PER_WARP + rr;
+            if (row0 + r >= row_end) break;  // uniform: rows of a tile are a prefix
+            const int tag = a.row_src[row0 + r];
+            __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(a.out_tbl[tag >> 24]);
+            const uint2 v = st8[(r * 16 + ((lane >> 1) ^ (r & 15))) * 2 + (lane & 1)];
+            *reinterpret_cast<uint2*>(obase + (int64_t)(tag & 0xFFFFFF) * a.H + col0 + lane * 4) = v;
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
         }
+      } else if (valid) {
+        const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
+        __nv_bfloat16* obase = a.out;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int col = nt * 256 + j * 128 + cg * TC_CW;
