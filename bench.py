@@ -155,8 +155,8 @@ def time_steps(fn, steps, warmup, barrier=None, finish=None):
 def launches_per_step(wl, T, world=1, ep="nccl"):
     P = T * wl["k"]
     if world > 1 and ep == "p2p":
-        # router, route, permute | counts exchange, plan, dispatch, barrier | tiles, 2 GEMMs, barrier | combine
-        n = 2 + (1 if P <= 1024 else 3) + 4 + 4 + 1
+        # router, route, permute | counts exchange, plan, dispatch, barrier | scales, tiles, 2 GEMMs, barrier | combine
+        n = 2 + (1 if P <= 1024 else 3) + 4 + 5 + 1
         if wl.get("shared"):
             n += (1 if T <= 1024 else 3) + 1 + 1 + 2
         return n

@@ -212,14 +212,16 @@ int b200moe_invert_permutation(int32_t* inv, const int32_t* perm, int64_t n, voi
  * No reference counterpart (the reference has no expert parallelism).  One process per GPU of one node; every
  * rank allocates the same set of buffers, exports them (CUDA IPC) and imports its peers' handles, then builds
  * device arrays of N pointers ("tables", entry r = rank r's buffer, the own entry being the own allocation).
- * A layer call is: exchange_counts -> plan -> dispatch -> barrier -> grouped_mlp_remote -> barrier -> combine;
+ * A layer call is: exchange_counts -> plan -> dispatch -> barrier -> transpose_scales -> grouped_mlp_remote ->
+ * barrier -> combine;
  * all data movement between GPUs is plain peer stores issued by those kernels, and the only waits are flag
  * barriers with a time limit (status bit 2).  `epoch` must grow by one with every barrier (exchange_counts
  * contains one) and take the same values on every rank.
  *
  * Buffers of one rank, for capacity C rows (C >= the most rows the rank can receive, e.g. N*T*k):
  *   flags   uint32 [8]            zero at start            cnt    int32 [N][E]
- *   xq      u8 [C][H]             xs_t   f32 [H/128][ld], ld >= C     src   int32 [C]   (the GEMM operands)
+ *   xq      u8 [C][H]             xs_rows f32 [C][H/128]              src   int32 [C]   (written by the peers)
+ *   xs_t    f32 [H/128][ld], ld >= C      (local: the scales in the layout the GEMMs read)
  *   y       bf16 [T*k][H]         per-slot results of the rank's OWN tokens, written by the expert owners */
 int b200moe_p2p_alloc(void** ptr, size_t bytes);                 /* device allocation, zero-filled */
 int b200moe_p2p_free(void* ptr);
@@ -236,12 +238,16 @@ int b200moe_ep_exchange_counts(const uint64_t* cnt_tbl, const uint64_t* flag_tbl
  * recv_offsets [E/N + 1]: expert_offsets of the rows this rank receives (local experts) */
 int b200moe_ep_plan(int32_t* dst_row0, int32_t* recv_offsets, const int32_t* cnt, int64_t E, int64_t N,
                     int64_t rank, void* stream);
-/* gather + 1x128 e4m3 quantisation of every (token,slot) row, stored into the owner rank's xq/xs_t/src
- * (src = rank << 24 | flat pair index t*k+j) */
+/* gather + 1x128 e4m3 quantisation of every (token,slot) row, stored into the owner rank's xq/xs_rows/src
+ * (xs_tbl holds the xs_rows buffers; src = rank << 24 | flat pair index t*k+j); H <= 8192 */
 int b200moe_ep_dispatch(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_t* src_tbl, const void* x,
                         const int32_t* sorted_pair, const int32_t* ids, const int32_t* expert_offsets,
                         const int32_t* dst_row0, int64_t T, int64_t k, int64_t H, int64_t E, int64_t N, int64_t rank,
-                        int64_t ld_remote, int64_t capacity, int32_t* status, void* stream);
+                        int64_t capacity, int32_t* status, void* stream);
+/* after the barrier that follows dispatch: xs_t[g][r] = xs_rows[r][g] for r < *n_rows (device value, e.g. the
+ * last entry of recv_offsets) */
+int b200moe_ep_transpose_scales(float* xs_t, int64_t ld, const float* xs_rows, const int32_t* n_rows, int64_t H,
+                                int64_t capacity, void* stream);
 /* b200moe_grouped_mlp on the received rows, each result row stored to out_tbl[src >> 24][(src & 0xFFFFFF), :].
  * R_capacity bounds the rows (the true count is read from expert_offsets on the device); tensor-core path only;
  * workspace as b200moe_grouped_mlp_workspace_bytes(R_capacity, ...). */

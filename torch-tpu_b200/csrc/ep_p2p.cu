@@ -8,7 +8,9 @@
 //                     (rows arrive already grouped by destination-local expert, sources in rank order) and
 //                     the expert_offsets of what it will receive
 //   dispatch          gather + 1x128 e4m3 quantise each (token,slot) row and store it STRAIGHT into the
-//                     destination's GEMM operand buffers (bytes, transposed scales, origin tag)    [+ barrier]
+//                     destination's buffers: bytes into the GEMM operand, the row's scales as one
+//                     contiguous run, the origin tag                                               [+ barrier]
+//   transpose scales  local: [row][K block] -> [K block][row], the layout the GEMM epilogue reads
 //   grouped MLP       the tcgen05 GEMMs on the received rows; the down GEMM's epilogue stores every result
 //                     row straight into the origin rank's per-slot buffer                          [+ barrier]
 //   combine           local weighted sum
@@ -107,16 +109,19 @@ __global__ void ep_plan_kernel(int32_t* __restrict__ dst_row0, int32_t* __restri
   }
 }
 
-// One warp per sorted position p: gather the token row, quantise 1x128 to e4m3, store bytes / transposed scales /
-// origin tag into the destination rank's buffers at the row the plan assigned.
+// One warp per sorted position p: gather the token row, quantise 1x128 to e4m3, store bytes / scales / origin tag
+// into the destination rank's buffers at the row the plan assigned.  Everything that crosses the link is a
+// contiguous run per warp instruction (256 B of row bytes, the row's H/128 scales); 4-byte stores scattered
+// ld_remote apart (the transposed scale layout) made the step several times slower at 8 ranks.
 __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_t* src_tbl,
                    const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ sorted_pair,
                    const int32_t* __restrict__ ids, const int32_t* __restrict__ offsets,
-                   const int32_t* __restrict__ dst_row0, int k, int El, int64_t P, int H, int64_t ld_remote,
-                   int64_t cap, int rank, int32_t* status) {
-  const int lane = threadIdx.x & 31;
-  const int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+                   const int32_t* __restrict__ dst_row0, int k, int El, int64_t P, int H, int64_t cap, int rank,
+                   int32_t* status) {
+  __shared__ float sc[8][64];
+  const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+  const int64_t p = (int64_t)blockIdx.x * 8 + wib;
   if (p < P) {
     const int pair = sorted_pair[p];
     const int e = ids[pair];
@@ -127,7 +132,7 @@ ep_dispatch_kernel(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_
     } else {
       const __nv_bfloat16* xr = x + (int64_t)(pair / k) * H;
       uint8_t* q = reinterpret_cast<uint8_t*>(xq_tbl[d]) + row * H;
-      float* s_t = reinterpret_cast<float*>(xs_tbl[d]);
+      float* s_rows = reinterpret_cast<float*>(xs_tbl[d]) + row * (H >> 7);
       for (int c0 = 0; c0 < H; c0 += 256) {
         const int c = c0 + lane * 8;
         float v[8];
@@ -152,13 +157,32 @@ ep_dispatch_kernel(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_
           o2.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
           o2.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
           *reinterpret_cast<uint2*>(q + c) = o2;
-          if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld_remote + row] = amax / kFp8Max;
+          if ((lane & 15) == 0) sc[wib][c >> 7] = amax / kFp8Max;
         }
       }
+      __syncwarp();
+      for (int g = lane; g < (H >> 7); g += 32) s_rows[g] = sc[wib][g];
       if (lane == 0) reinterpret_cast<int32_t*>(src_tbl[d])[row] = (rank << 24) | pair;
     }
   }
   __threadfence_system();
+}
+
+// xs_t[g][row] = xs_rows[row][g] for the rows received in this call (their count sits on the device)
+__global__ void __launch_bounds__(256)
+ep_transpose_scales_kernel(float* __restrict__ xs_t, int64_t ld, const float* __restrict__ xs_rows,
+                           const int32_t* __restrict__ n_rows, int nH) {
+  __shared__ float tile[32][65];
+  const int R = *n_rows;
+  const int64_t r0 = (int64_t)blockIdx.x * 32;
+  if (r0 >= R) return;
+  const int rows = (int)((R - r0) < 32 ? (R - r0) : 32);
+  for (int i = threadIdx.x; i < rows * nH; i += blockDim.x) tile[i / nH][i % nH] = xs_rows[r0 * nH + i];
+  __syncthreads();
+  for (int i = threadIdx.x; i < nH * 32; i += blockDim.x) {
+    const int g = i >> 5, r = i & 31;
+    if (r < rows) xs_t[(int64_t)g * ld + r0 + r] = tile[r][g];
+  }
 }
 
 int check_table_args(const void* tbl, int64_t N, int64_t rank) {
@@ -230,18 +254,27 @@ extern "C" int b200moe_ep_plan(int32_t* dst_row0, int32_t* recv_offsets, const i
 extern "C" int b200moe_ep_dispatch(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_t* src_tbl,
                                    const void* x, const int32_t* sorted_pair, const int32_t* ids,
                                    const int32_t* expert_offsets, const int32_t* dst_row0, int64_t T, int64_t k,
-                                   int64_t H, int64_t E, int64_t N, int64_t rank, int64_t ld_remote,
-                                   int64_t capacity, int32_t* status, void* stream) {
+                                   int64_t H, int64_t E, int64_t N, int64_t rank, int64_t capacity,
+                                   int32_t* status, void* stream) {
   int rc = check_table_args(xq_tbl, N, rank);
   if (rc) return rc;
   MOE_CHECK_ARG(xs_tbl && src_tbl && x && sorted_pair && ids && expert_offsets && dst_row0);
-  MOE_CHECK_ARG(T >= 0 && k > 0 && H > 0 && E > 0 && capacity > 0 && ld_remote >= capacity);
-  MOE_CHECK_SHAPE(H % kBlock == 0 && E % N == 0 && T * k < (1 << 24));
+  MOE_CHECK_ARG(T >= 0 && k > 0 && H > 0 && E > 0 && capacity > 0);
+  MOE_CHECK_SHAPE(H % kBlock == 0 && H <= 64 * kBlock && E % N == 0 && T * k < (1 << 24));
   if (!moe_aligned16(x)) return B200MOE_EALIGN;
   const int64_t P = T * k;
   if (P == 0) return B200MOE_OK;
   ep_dispatch_kernel<<<(unsigned)((P + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
       xq_tbl, xs_tbl, src_tbl, reinterpret_cast<const __nv_bfloat16*>(x), sorted_pair, ids, expert_offsets, dst_row0,
-      (int)k, (int)(E / N), P, (int)H, ld_remote, capacity, (int)rank, status);
+      (int)k, (int)(E / N), P, (int)H, capacity, (int)rank, status);
+  return moe_launch_status();
+}
+
+extern "C" int b200moe_ep_transpose_scales(float* xs_t, int64_t ld, const float* xs_rows, const int32_t* n_rows,
+                                           int64_t H, int64_t capacity, void* stream) {
+  MOE_CHECK_ARG(xs_t && xs_rows && n_rows && H > 0 && capacity > 0 && ld >= capacity);
+  MOE_CHECK_SHAPE(H % kBlock == 0 && H <= 64 * kBlock);
+  ep_transpose_scales_kernel<<<(unsigned)((capacity + 31) / 32), 256, 0, (cudaStream_t)stream>>>(
+      xs_t, ld, xs_rows, n_rows, (int)(H / kBlock));
   return moe_launch_status();
 }

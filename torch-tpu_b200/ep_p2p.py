@@ -102,12 +102,13 @@ class P2PFusedMoE:
         self.ld = _round_up(self.cap, 128)
         nH = self.H // 128
         self.arena = PeerArena([("flags", 256), ("cnt", self.N * self.E * 4), ("xq", self.cap * self.H),
-                                ("xs", nH * self.ld * 4), ("src", self.cap * 4),
+                                ("xs_rows", self.cap * nH * 4), ("src", self.cap * 4),
                                 ("y", max_tokens * self.k * self.H * 2)], self.dev, group)
         a = self.arena
         self.cnt = a.local("cnt", torch.int32, (self.N, self.E))
         self.xq = a.local("xq", torch.uint8, (self.cap, self.H))
-        self.xs = a.local("xs", torch.float32, (nH, self.ld))
+        self.xs_rows = a.local("xs_rows", torch.float32, (self.cap, nH))
+        self.xs = torch.empty(nH, self.ld, dtype=torch.float32, device=self.dev)   # local: the GEMMs' layout
         self.src = a.local("src", torch.int32, (self.cap,))
         self.y = a.local("y", torch.bfloat16, (max_tokens, self.k, self.H))
         self.dst_row0 = torch.empty(self.E, dtype=torch.int32, device=self.dev)
@@ -118,10 +119,17 @@ class P2PFusedMoE:
         self.workspace = torch.empty(need + 256, dtype=torch.uint8, device=self.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.epoch = 0
+        self.phase_events = None   # set to [] to have forward() record (name, event) after every phase
 
     def _next_epoch(self):
         self.epoch = (self.epoch + 1) & 0xFFFFFFFF
         return ctypes.c_uint32(self.epoch)
+
+    def _mark(self, name):
+        if self.phase_events is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self.phase_events.append((name, e))
 
     def forward(self, x):
         layer, a, lib = self.layer, self.arena, L.lib()
@@ -130,17 +138,24 @@ class P2PFusedMoE:
             raise ValueError("x must be [T <= max_tokens, hidden]")
         N, rank, E = self.N, self.rank, self.E
         p, st = ops._ptr, ops._stream
+        self._mark("start")
         ids, w = layer.route(x)                                    # ids over GLOBAL experts
         sorted_pair, offsets = ops.permute(ids, E, status=self.status)
+        self._mark("route+permute")
         L.check(lib.b200moe_ep_exchange_counts(p(a.table("cnt")), p(a.table("flags")), p(offsets), E, N, rank,
                                                self._next_epoch(), p(self.status), st()), "b200moe_ep_exchange_counts")
         L.check(lib.b200moe_ep_plan(p(self.dst_row0), p(self.recv_offsets), p(self.cnt), E, N, rank, st()),
                 "b200moe_ep_plan")
-        L.check(lib.b200moe_ep_dispatch(p(a.table("xq")), p(a.table("xs")), p(a.table("src")), p(x), p(sorted_pair),
-                                        p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank, self.ld,
+        self._mark("counts+plan")
+        L.check(lib.b200moe_ep_dispatch(p(a.table("xq")), p(a.table("xs_rows")), p(a.table("src")), p(x),
+                                        p(sorted_pair), p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank,
                                         self.cap, p(self.status), st()), "b200moe_ep_dispatch")
+        self._mark("dispatch")
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
                 "b200moe_p2p_barrier")
+        self._mark("barrier")
+        L.check(lib.b200moe_ep_transpose_scales(p(self.xs), self.ld, p(self.xs_rows), p(self.recv_offsets[self.El:]),
+                                                H, self.cap, st()), "b200moe_ep_transpose_scales")
         wg, wu, wd, sg, su, sd = layer.w
         base = (self.workspace.data_ptr() + 255) // 256 * 256
         avail = self.workspace.numel() - (base - self.workspace.data_ptr())
@@ -149,14 +164,19 @@ class P2PFusedMoE:
                                                ops._DT[sg.dtype], self.cap, H, self.I, self.El,
                                                ctypes.c_void_p(base), avail, p(self.status), st()),
                 "b200moe_grouped_mlp_remote")
+        self._mark("grouped_mlp")
         add = None
         if layer.shared is not None:                               # local work between the two barriers
             out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
             ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
             add = out1.view(T, H)
+            self._mark("shared")
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
                 "b200moe_p2p_barrier")
-        return ops.combine(self.y[:T], w, add=add)
+        self._mark("barrier2")
+        out = ops.combine(self.y[:T], w, add=add)
+        self._mark("combine")
+        return out
 
     __call__ = forward
 

@@ -68,7 +68,8 @@ SIGNATURES = {
     "b200moe_ep_exchange_counts": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_uint32, c_void_p,
                                            c_void_p]),
     "b200moe_ep_plan": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
-    "b200moe_ep_dispatch": (c_int, [c_void_p] * 8 + [c_int64] * 8 + [c_void_p, c_void_p]),
+    "b200moe_ep_dispatch": (c_int, [c_void_p] * 8 + [c_int64] * 7 + [c_void_p, c_void_p]),
+    "b200moe_ep_transpose_scales": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200moe_grouped_mlp_remote": (c_int, [c_void_p] * 12 + [c_int, c_int64, c_int64, c_int64, c_int64, c_void_p,
                                                              c_size_t, c_void_p, c_void_p]),
 }
