@@ -211,11 +211,19 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
+// 16-byte asynchronous copy global -> shared; bytes = 0 writes zeros (rows / columns past the end)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gsrc), "r"(bytes)
+               : "memory");
+}
+
 __global__ void __launch_bounds__(128)
 router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int64_t E) {
-  __shared__ __align__(16) __nv_bfloat16 sA[RG_BM * RG_LD];
-  __shared__ __align__(16) __nv_bfloat16 sB[RG_BN * RG_LD];
+  // two stages: the copies of K chunk kt+1 are in flight while the MMAs of chunk kt run
+  __shared__ __align__(16) __nv_bfloat16 sA[2][RG_BM * RG_LD];
+  __shared__ __align__(16) __nv_bfloat16 sB[2][RG_BN * RG_LD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int64_t t0 = (int64_t)blockIdx.x * RG_BM, e0 = (int64_t)blockIdx.y * RG_BN;
   float acc[RG_BN / 8][4];
@@ -224,23 +232,34 @@ router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   const int g = lane >> 2, tq = lane & 3;
-  for (int64_t k0 = 0; k0 < H; k0 += RG_BK) {
+  auto load_stage = [&](int st, int64_t k0) {
     // 64 rows x 64 bf16 = 512 chunks of 16 B per operand; 128 threads x 4
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      int c = tid + i * 128;
-      int r = c >> 3, cc = (c & 7) * 8;
-      uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
-      if (t0 + r < T && k0 + cc < H) va = *reinterpret_cast<const uint4*>(x + (t0 + r) * H + k0 + cc);
-      if (e0 + r < E && k0 + cc < H) vb = *reinterpret_cast<const uint4*>(wr + (e0 + r) * H + k0 + cc);
-      *reinterpret_cast<uint4*>(sA + r * RG_LD + cc) = va;
-      *reinterpret_cast<uint4*>(sB + r * RG_LD + cc) = vb;
+      const int c = tid + i * 128;
+      const int r = c >> 3, cc = (c & 7) * 8;
+      const bool ka = k0 + cc < H;
+      const bool oka = ka && t0 + r < T, okb = ka && e0 + r < E;
+      cp_async16(sA[st] + r * RG_LD + cc, oka ? x + (t0 + r) * H + k0 + cc : x, oka ? 16 : 0);
+      cp_async16(sB[st] + r * RG_LD + cc, okb ? wr + (e0 + r) * H + k0 + cc : wr, okb ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int nk = (int)((H + RG_BK - 1) / RG_BK);
+  load_stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int st = kt & 1;
+    if (kt + 1 < nk) {
+      load_stage(st ^ 1, (int64_t)(kt + 1) * RG_BK);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < RG_BK; kk += 16) {
       uint32_t a[4];
-      const __nv_bfloat16* pa = sA + (warp * 16 + g) * RG_LD + kk + tq * 2;
+      const __nv_bfloat16* pa = sA[st] + (warp * 16 + g) * RG_LD + kk + tq * 2;
       a[0] = *reinterpret_cast<const uint32_t*>(pa);
       a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * RG_LD);
       a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
@@ -248,13 +267,13 @@ router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
 #pragma unroll
       for (int nb = 0; nb < RG_BN / 8; ++nb) {
         uint32_t b[2];
-        const __nv_bfloat16* pb = sB + (nb * 8 + g) * RG_LD + kk + tq * 2;
+        const __nv_bfloat16* pb = sB[st] + (nb * 8 + g) * RG_LD + kk + tq * 2;
         b[0] = *reinterpret_cast<const uint32_t*>(pb);
         b[1] = *reinterpret_cast<const uint32_t*>(pb + 8);
         mma_bf16_16816(acc[nb], a, b);
       }
     }
-    __syncthreads();
+    __syncthreads();  // the stage is overwritten by the copies issued at the top of the next iteration
   }
 #pragma unroll
   for (int nb = 0; nb < RG_BN / 8; ++nb) {
