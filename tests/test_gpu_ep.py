@@ -87,3 +87,40 @@ def test_ep_cuda_path(world, mode):
     for p in procs:
         p.join(timeout=60)
     assert all(r[1] for r in res), res
+
+
+def test_ep_plan_tiles_every_destination_buffer():
+    """b200moe_ep_plan for every rank of an 8-rank job on one GPU (the plan needs only the count matrix): the row
+    ranges the ranks are given on each destination are disjoint, in (local expert, source rank) order, and end at the
+    destination's own recv_offsets."""
+    import ctypes
+    import numpy as np
+    sys.path.insert(0, ROOT)
+    import torch_tpu_b200  # noqa: F401
+    from torch_tpu_b200 import lib as L
+    lib = L.lib()
+    N, E = 8, 256
+    El = E // N
+    rng = np.random.default_rng(3)
+    cnt = rng.integers(0, 300, size=(N, E)).astype(np.int32)
+    cnt[:, 5] = 0                                    # an expert nobody routes to
+    cnt_d = torch.from_numpy(cnt).cuda()
+    dst = torch.empty(N, E, dtype=torch.int32, device="cuda")
+    rcv = torch.empty(N, El + 1, dtype=torch.int32, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for r in range(N):
+        L.check(lib.b200moe_ep_plan(ctypes.c_void_p(dst[r].data_ptr()), ctypes.c_void_p(rcv[r].data_ptr()),
+                                    ctypes.c_void_p(cnt_d.data_ptr()), E, N, r, st), "b200moe_ep_plan")
+    torch.cuda.synchronize()
+    dst, rcv = dst.cpu().numpy(), rcv.cpu().numpy()
+    tot = cnt.sum(0)
+    for d in range(N):
+        want_off = np.concatenate([[0], np.cumsum(tot[d * El:(d + 1) * El])])
+        assert np.array_equal(rcv[d], want_off)
+        pos = 0
+        for le in range(El):
+            e = d * El + le
+            for r in range(N):                       # inside an expert: sources in rank order, back to back
+                assert dst[r, e] == pos, (d, le, r)
+                pos += cnt[r, e]
+        assert pos == rcv[d, El]
