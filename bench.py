@@ -372,7 +372,7 @@ def main():
                 xx = [make_x(Ts, wl["H"], dev, seed=300 + i).to(dev) for i in range(4)]
                 j = [0]
 
-                use_graph = Ts <= 64   # decode sizes: one graph launch instead of a dozen small ones
+                use_graph = Ts <= 1024   # launch-bound sizes: one graph launch instead of a dozen small ones
 
                 def st():
                     (layer.forward_graph if use_graph else layer.forward)(xx[j[0] % 4])
