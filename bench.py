@@ -34,6 +34,12 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel (gate/up GEMM) at the headline
+# size, taken from an ncu capture of this very command (profiles/moe_gemm_tc_dram_traffic.md); bench.py cannot run ncu
+# itself, so the figure is carried here and is null for sizes that were not captured.
+NCU_TRAFFIC_BYTES = {("mixtral", 4096): 1295.8e6}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -354,7 +360,9 @@ def main():
         else:
             roof = {"bound": "hbm", "achieved": b_g1 / (ms_g1 / 1000) / 1e9, "peak": peaks["hbm"], "unit": "GB/s"}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = None
+        roof["traffic"] = NCU_TRAFFIC_BYTES.get((args.workload, T))
+        roof["traffic_unit"] = "bytes per launch (ncu dram read + write)"
+        roof["algorithmic_bytes"] = b_g1
         roof["kernel"] = "moe_gemm_tc_kernel<false> (gate/up GEMM + SiLU*up + requantise)"
         roof["ms_per_launch"] = ms_g1
         roof["peak_source"] = (f"{peaks['src']}: FP8 dense taken as 2 x the bf16 cuBLAS burst figure"

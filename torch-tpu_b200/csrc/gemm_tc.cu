@@ -105,6 +105,7 @@ struct TcArgs {
   const uint64_t* out_tbl;  // ... and the per-rank output buffers (device array of pointers)
   int H, I, NT;
   int KS;        // K splits (down GEMM of decode-size batches); 1 = none
+  int m_major;   // work-item order: 0 = n-tile slow, m-tile fast; 1 = m-tile slow, n-tile fast (see launch_tc)
   float* out32;  // fp32 accumulation target when KS > 1
   uint8_t* hq;
   float* hs_t;
@@ -293,7 +294,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       PROF_DECL(p_wait);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int ks = t % a.KS, tt = t / a.KS;
-        const int nt = tt / num_mtiles, mt = tt - nt * num_mtiles;
+        const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
         const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
         const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
@@ -387,7 +388,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     PROF_T0(e_t0);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const int ks = t % a.KS, tt = t / a.KS;
-      const int nt = tt / num_mtiles, mt = tt - nt * num_mtiles;
+      const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
       const int row_end = a.offsets[e + 1];
       const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
@@ -673,6 +674,18 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.I = g.I;
   a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
   a.KS = (GEMM2 && g.ksplit > 1 && g.out32 && !g.row_src) ? g.ksplit : 1;
+  // Work-item order.  The CTAs that run together hold about one SM count of consecutive work items.  With the
+  // n-tile as the slow index they share a few weight tiles and sweep ALL rows of A once per group of n-tiles: right
+  // while A stays in L2.  When A is larger than that (prefill-size down GEMM: P x I bytes; many-token gate/up GEMM
+  // with small experts), the m-tile becomes the slow index: an m-tile's rows are read once, by the CTAs of all its
+  // n-tiles at the same time, and an expert's weights are shared by its consecutive m-tiles through L2 as long as
+  // one expert's weights for this GEMM fit there.  Measured on the Mixtral down GEMM at 4096 tokens: DRAM reads
+  // 1.43 GB with the n-tile slow (hq re-read 7x), against 0.59 GB algorithmic.
+  {
+    const double a_bytes = (double)g.P * K;
+    const double w_expert = (double)(GEMM2 ? g.H : 2 * g.I) * K;
+    a.m_major = (a_bytes > 48e6 && w_expert <= 64e6) ? 1 : 0;
+  }
   a.out32 = g.out32;
   a.hq = g.hq;
   a.hs_t = g.hs_t;
