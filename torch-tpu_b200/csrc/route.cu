@@ -289,20 +289,21 @@ router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
   }
 }
 
-// Small-T variant (decode): one warp per expert row streams wr[e,:] once with 16-byte loads and dots it
-// with up to RV_MAXT token rows; the grid covers all experts so the read is spread over many SMs.
+// Small-T variant (decode): one block per expert row; its 4 warps split H (16-byte loads) and dot the slice with up
+// to RV_MAXT token rows; the warps' partial sums are added in warp order (deterministic).  The grid covers all
+// experts, so the read of the router weights is spread over many SMs and only H/1024 loads deep.
 constexpr int RV_MAXT = 8;
 __global__ void __launch_bounds__(128)
 router_gemv_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int64_t E) {
-  const int lane = threadIdx.x & 31;
-  const int64_t e = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  __shared__ float part[4][RV_MAXT];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t e = blockIdx.x;
   const int64_t t0 = (int64_t)blockIdx.y * RV_MAXT;
-  if (e >= E) return;
   float acc[RV_MAXT];
 #pragma unroll
   for (int t = 0; t < RV_MAXT; ++t) acc[t] = 0.f;
-  for (int64_t h = lane * 8; h < H; h += 256) {
+  for (int64_t h = (int64_t)threadIdx.x * 8; h < H; h += 1024) {
     uint4 wv = *reinterpret_cast<const uint4*>(wr + e * H + h);
     const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
@@ -324,8 +325,11 @@ router_gemv_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
     float v = acc[t];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    if (lane == 0 && t0 + t < T) logits[(t0 + t) * E + e] = v;
+    if (lane == 0) part[warp][t] = v;
   }
+  __syncthreads();
+  if (threadIdx.x < RV_MAXT && t0 + threadIdx.x < T)
+    logits[(t0 + threadIdx.x) * E + e] = part[0][threadIdx.x] + part[1][threadIdx.x] + part[2][threadIdx.x] + part[3][threadIdx.x];
 }
 
 constexpr int RS_TOK = 4, RS_WARPS = 8;
@@ -467,7 +471,7 @@ extern "C" int b200moe_router_logits(float* logits, const void* x, const void* w
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto wb = reinterpret_cast<const __nv_bfloat16*>(wr);
   if (T <= 2 * RV_MAXT) {
-    dim3 grid((unsigned)((E + 3) / 4), (unsigned)((T + RV_MAXT - 1) / RV_MAXT));
+    dim3 grid((unsigned)E, (unsigned)((T + RV_MAXT - 1) / RV_MAXT));
     router_gemv_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(logits, xb, wb, T, H, E);
   } else if (E <= 16) {
     const unsigned grid = (unsigned)((T + RS_TOK - 1) / RS_TOK);
