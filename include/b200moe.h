@@ -208,6 +208,15 @@ int b200moe_ep_unpack_rows(uint8_t* xq, float* xs_t, int64_t ld, const uint8_t* 
 /* inv[perm[i]] = i */
 int b200moe_invert_permutation(int32_t* inv, const int32_t* perm, int64_t n, void* stream);
 
+/* ---- FP8 block-scaled linear layer ----------------------------------------------------------------------
+ * out[M,N] (bf16) = x[M,K] (bf16, quantised per row per 128 columns to e4m3 on the fly) . dequant(w)^T with
+ * w [N,K] e4m3 and scale [ceil(N/128), K/128] (fp32 or bf16): the expert GEMM with one expert, no activation
+ * and the tensor-core path only.  Stands in for tpudnnMmW8A16DqAsync behind my_ops.mm_w8a16_dq_forward
+ * (my_ops/MmW8A16Dq.cpp:185-229), with activations in FP8 instead of bf16.  K % 128 == 0, N % 64 == 0. */
+size_t b200moe_linear_workspace_bytes(int64_t M, int64_t K, int64_t N, int scale_dtype);
+int b200moe_linear_w8(void* out, const void* x, const void* w, const void* scale, int scale_dtype, int64_t M,
+                      int64_t K, int64_t N, void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
+
 /* ---- expert parallelism over peer memory (NVLink) --------------------------------------------------
  * No reference counterpart (the reference has no expert parallelism).  One process per GPU of one node; every
  * rank allocates the same set of buffers, exports them (CUDA IPC) and imports its peers' handles, then builds

@@ -155,3 +155,29 @@ def test_layer_end_to_end(m, cfgname, T):
     layer.host_join()
     torch.cuda.synchronize()
     assert same(oh, y.cpu())
+
+
+@pytest.mark.parametrize("M,K,N", [(32, 7168, 1536), (32, 7168, 576), (32, 2048, 7168), (64, 4096, 2048),
+                                   (300, 512, 320)])
+def test_mm_w8a16_dq_forward(m, M, K, N):
+    """Dense block-scaled linear layer through the reference's op name, on the reference's own shapes and input
+    distributions (python/regression/test_llm/test_mm_w8a16_dq.py:101-140: randn activations, randn weights cast to
+    e4m3, randn bf16 scales).  Expected value: the reference's CPU function (dequantise the weight block-wise,
+    F.linear) on the activations as the kernel sees them (quantised 1x128, tolerance of the FP8 path), and the
+    reference's own acceptance metric against the unquantised activations."""
+    g = torch.Generator().manual_seed(M + K + N)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, generator=g).to(torch.float8_e4m3fn)
+    s = torch.randn((N + 127) // 128, (K + 127) // 128, generator=g).to(torch.bfloat16)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    r = torch.ops.my_ops.mm_w8a16_dq_forward(x.to(DEV), w.to(DEV), s.to(DEV), out, 128)
+    assert r.data_ptr() == out.data_ptr()
+    wd = (w.float().view(-1) .view(N, K))
+    sb = s.float().repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    wdq = wd * sb                                           # fp32 dequantised weight
+    xq, xs = O.quant_act_1x128(x)
+    want_q = O.dequant_act(xq, xs).double() @ wdq.double().T
+    met = O.parity_metrics(out.cpu(), want_q)
+    assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+    want_ref = x.float().double() @ wdq.double().T          # the reference's arithmetic: bf16 activations
+    assert O.cos_sim(out.cpu().float().numpy(), want_ref.numpy()) > 0.99

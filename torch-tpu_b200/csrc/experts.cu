@@ -489,6 +489,99 @@ extern "C" int b200moe_grouped_mlp_remote(const uint64_t* out_tbl, const int32_t
                           workspace_bytes, status, stream);
 }
 
+// ---- plain FP8 block-scaled linear layer -----------------------------------------------------------------
+namespace {
+struct LinLayout {
+  size_t offsets, mtiles, nmt, xq, xs, sc32, total;
+  int64_t ld;
+  int max_mtiles;
+};
+LinLayout lin_layout(int64_t M, int64_t K, int64_t N, int scale_dtype) {
+  LinLayout L{};
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = o;
+    o = (o + bytes + 255) & ~(size_t)255;
+    return at;
+  };
+  L.ld = (M + kTileM - 1) / kTileM * kTileM;
+  if (L.ld == 0) L.ld = kTileM;
+  L.max_mtiles = (int)(L.ld / kTileM);
+  L.offsets = take(2 * sizeof(int32_t));
+  L.mtiles = take((size_t)L.max_mtiles * 2 * sizeof(int32_t));
+  L.nmt = take(sizeof(int32_t));
+  L.xq = take((size_t)L.ld * K);
+  L.xs = take((size_t)(K / kBlock) * L.ld * sizeof(float));
+  L.sc32 = take(scale_dtype == B200MOE_BF16 ? (size_t)((N + kBlock - 1) / kBlock) * (K / kBlock) * sizeof(float) : 0);
+  L.total = o;
+  return L;
+}
+__global__ void scales1_to_f32_kernel(float* __restrict__ dst, const __nv_bfloat16* __restrict__ s, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __bfloat162float(s[i]);
+}
+}  // namespace
+
+extern "C" size_t b200moe_linear_workspace_bytes(int64_t M, int64_t K, int64_t N, int scale_dtype) {
+  if (M < 0 || K <= 0 || N <= 0 || K % kBlock || N % 64) return 0;
+  return lin_layout(M, K, N, scale_dtype).total;
+}
+
+extern "C" int b200moe_linear_w8(void* out, const void* x, const void* w, const void* scale, int scale_dtype,
+                                 int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes,
+                                 int32_t* status, void* stream) {
+  MOE_CHECK_ARG(M >= 0 && K > 0 && N > 0);
+  MOE_CHECK_ARG(scale_dtype == B200MOE_F32 || scale_dtype == B200MOE_BF16);
+  MOE_CHECK_SHAPE(K % kBlock == 0 && N % 64 == 0 && M < (1 << 24) && N < (int64_t(1) << 31));
+  if (M == 0) return B200MOE_OK;
+  MOE_CHECK_ARG(out && x && w && scale);
+  if (!moe_aligned16(out) || !moe_aligned16(x) || !moe_aligned16(w)) return B200MOE_EALIGN;
+  if (!moe_tc_available()) return B200MOE_EDRIVER;
+  const LinLayout L = lin_layout(M, K, N, scale_dtype);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return B200MOE_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = reinterpret_cast<char*>(workspace);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + L.offsets);
+  int32_t* mtiles = reinterpret_cast<int32_t*>(ws + L.mtiles);
+  int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
+  int rc = moe_fill_identity_offsets(offsets, M, st);
+  if (rc) return rc;
+  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, st);
+  if (rc) return rc;
+  rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.xq), reinterpret_cast<float*>(ws + L.xs), L.ld, x, nullptr,
+                          1, M, K, stream);
+  if (rc) return rc;
+  const void* sc = scale;
+  if (scale_dtype == B200MOE_BF16) {
+    const int64_t n = ((N + kBlock - 1) / kBlock) * (K / kBlock);
+    scales1_to_f32_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(
+        reinterpret_cast<float*>(ws + L.sc32), reinterpret_cast<const __nv_bfloat16*>(scale), n);
+    rc = moe_launch_status();
+    if (rc) return rc;
+    sc = ws + L.sc32;
+  }
+  MoeGemmArgs g{};
+  g.aq = reinterpret_cast<const uint8_t*>(ws + L.xq);
+  g.as_t = reinterpret_cast<const float*>(ws + L.xs);
+  g.ld = L.ld;
+  g.div = 1;
+  g.w0 = reinterpret_cast<const uint8_t*>(w);
+  g.s0 = sc;
+  g.scale_dtype = B200MOE_F32;
+  g.mtiles = mtiles;
+  g.num_mtiles = nmt;
+  g.offsets = offsets;
+  g.max_mtiles = L.max_mtiles;
+  g.P = M;
+  g.H = (int)K;
+  g.I = (int)N;
+  g.E = 1;
+  g.out = reinterpret_cast<__nv_bfloat16*>(out);
+  g.status = status;
+  return moe_linear_tc(g, st);
+}
+
 extern "C" int b200moe_abi_version(void) { return B200MOE_ABI_VERSION; }
 
 extern "C" const char* b200moe_error_string(int code) {

@@ -247,10 +247,13 @@ __host__ __device__ constexpr uint32_t make_idesc(int b_mn_major) {
   return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-template <bool GEMM2>
+// MODE 0 = gate/up GEMM (+ SiLU*up + requantise), 1 = down GEMM, 2 = plain linear layer: out[r, :N] = A[r, :K] W^T with
+// W [N, K] K-major (the gate/up operand path with the down GEMM's bf16 store; a.I = N, a.H = K, 256 outputs per tile)
+template <int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB0,
                    const __grid_constant__ CUtensorMap tmB1, const TcArgs a) {
+  constexpr bool GEMM2 = MODE == 1, DENSE = MODE == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   TcShared* sh = reinterpret_cast<TcShared*>(smem + (size_t)TC_STAGES * TC_STAGE_BYTES);
@@ -315,7 +318,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           mbar_arrive_expect_tx(full, DBG(4) ? TC_A_BYTES : TC_STAGE_BYTES);
           tma_load_2d(sa, &tmA, kb * kBlock, row0, full);
           if (DBG(4)) continue;
-          if (!GEMM2) {
+          if (DENSE) {
+            tma_load_2d(sb, &tmB0, kb * kBlock, e * a.I + nt * 256, full);
+            tma_load_2d(sb + 128 * 128, &tmB0, kb * kBlock, e * a.I + nt * 256 + 128, full);
+          } else if (!GEMM2) {
             tma_load_2d(sb, &tmB0, kb * kBlock, e * a.I + nt * 128, full);
             tma_load_2d(sb + 128 * 128, &tmB1, kb * kBlock, e * a.I + nt * 128, full);
           } else {
@@ -408,8 +414,12 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const float* const S0 = reinterpret_cast<const float*>(a.s0);
       const float* const S1 = GEMM2 ? S0 : reinterpret_cast<const float*>(a.s1);
       const int sstep = GEMM2 ? nH : 1;
-      const int64_t w0i = (GEMM2 ? (int64_t)e * nI * nH + 2 * nt : ((int64_t)e * nI + nt) * nH) + (int64_t)kb0 * sstep;
-      const int64_t w1i = w0i + (GEMM2 ? ((2 * nt + 1 < nH) ? 1 : 0) : 0);
+      const int nIs = (a.I + kBlock - 1) / kBlock;  // scale rows of one expert (= nI unless a linear layer's N % 128 != 0)
+      const int64_t w0i = (GEMM2   ? (int64_t)e * nI * nH + 2 * nt
+                           : DENSE ? ((int64_t)e * nIs + 2 * nt) * nH
+                                   : ((int64_t)e * nI + nt) * nH) +
+                          (int64_t)kb0 * sstep;
+      const int64_t w1i = w0i + (GEMM2 ? ((2 * nt + 1 < nH) ? 1 : 0) : DENSE ? ((2 * nt + 1 < nIs) ? nH : 0) : 0);
       auto load_sa = [&](int kb) { return valid ? a.as_t[(int64_t)(kb0 + kb) * a.ld + grow] : 0.f; };
       // scales are fetched two K blocks ahead (the activation-scale lines come from L2)
       float sa0 = load_sa(0), sa1 = KB > 1 ? load_sa(1) : 0.f;
@@ -482,7 +492,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       if (!ok) break;
       PROF_T0(te);
       if (DBG(2)) continue;
-      if (!GEMM2) {
+      if (MODE == 0) {
         // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over TC_CG warps
         float amax = 0.f;
 #pragma unroll
@@ -553,19 +563,20 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       } else if (valid) {
         const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
         __nv_bfloat16* obase = a.out;
+        const int OUTW = DENSE ? a.I : a.H;  // columns of an output row
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int col = nt * 256 + j * 128 + cg * TC_CW;
-          if (col < a.H && a.KS > 1) {  // K split: partial sums meet in the fp32 buffer
-            float* dst32 = a.out32 + dstrow * a.H + col;
+          if (col < OUTW && a.KS > 1) {  // K split: partial sums meet in the fp32 buffer
+            float* dst32 = a.out32 + dstrow * OUTW + col;
 #pragma unroll
             for (int w = 0; w < TC_CW / 2; ++w) {
               const float2 v = unpack2(acc[j][w]);
               atomicAdd(dst32 + 2 * w, v.x);
               atomicAdd(dst32 + 2 * w + 1, v.y);
             }
-          } else if (col < a.H) {
-            uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * a.H + col);
+          } else if (col < OUTW) {
+            uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * OUTW + col);
 #pragma unroll
             for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
               uint4 o;
@@ -651,14 +662,15 @@ int device_sm_count() {
   return n;
 }
 
-template <bool GEMM2>
+template <int MODE>
 int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
+  constexpr bool GEMM2 = MODE == 1, DENSE = MODE == 2;
   if (g.scale_dtype != B200MOE_F32) return B200MOE_EINVAL;  // the caller converts bf16 scales first
   const int K = GEMM2 ? g.I : g.H;
   CUtensorMap tmA, tmB0, tmB1;
   if (!make_map_u8(&tmA, g.aq, (uint64_t)g.P, (uint64_t)K)) return B200MOE_EDRIVER;
   if (!make_map_u8(&tmB0, g.w0, (uint64_t)g.E * g.I, (uint64_t)g.H)) return B200MOE_EDRIVER;
-  if (!make_map_u8(&tmB1, GEMM2 ? g.w0 : g.w1, (uint64_t)g.E * g.I, (uint64_t)g.H)) return B200MOE_EDRIVER;
+  if (!make_map_u8(&tmB1, (GEMM2 || DENSE) ? g.w0 : g.w1, (uint64_t)g.E * g.I, (uint64_t)g.H)) return B200MOE_EDRIVER;
   TcArgs a{};
   a.as_t = g.as_t;
   a.ld = g.ld;
@@ -672,7 +684,7 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.out_tbl = g.out_tbl;
   a.H = g.H;
   a.I = g.I;
-  a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
+  a.NT = GEMM2 ? (g.H + 255) / 256 : DENSE ? (g.I + 255) / 256 : g.I / 128;
   a.KS = (GEMM2 && g.ksplit > 1 && g.out32 && !g.row_src) ? g.ksplit : 1;
   // Work-item order.  The CTAs that run together hold about one SM count of consecutive work items.  With the
   // n-tile as the slow index they share a few weight tiles and sweep ALL rows of A once per group of n-tiles: right
@@ -683,7 +695,7 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   // 1.43 GB with the n-tile slow (hq re-read 7x), against 0.59 GB algorithmic.
   {
     const double a_bytes = (double)g.P * K;
-    const double w_expert = (double)(GEMM2 ? g.H : 2 * g.I) * K;
+    const double w_expert = (double)(GEMM2 ? g.H : DENSE ? g.I : 2 * g.I) * K;
     a.m_major = (a_bytes > 48e6 && w_expert <= 64e6) ? 1 : 0;
   }
   a.out32 = g.out32;
@@ -696,13 +708,14 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
 #endif
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(moe_gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
-    cudaFuncSetAttribute(moe_gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+    cudaFuncSetAttribute(moe_gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+    cudaFuncSetAttribute(moe_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
+    cudaFuncSetAttribute(moe_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
     attr = true;
   }
   const long long max_tiles = (long long)g.max_mtiles * a.NT * a.KS;
   const int grid = (int)(max_tiles < device_sm_count() ? max_tiles : device_sm_count());
-  moe_gemm_tc_kernel<GEMM2><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
+  moe_gemm_tc_kernel<MODE><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
   return moe_launch_status();
 }
 
@@ -742,5 +755,6 @@ int moe_f32_rows_to_bf16(__nv_bfloat16* out, const float* in, int64_t n, cudaStr
 
 int moe_device_sm_count() { return device_sm_count(); }
 
-int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<false>(a, st); }
-int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<true>(a, st); }
+int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<0>(a, st); }
+int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<1>(a, st); }
+int moe_linear_tc(const MoeGemmArgs& a, cudaStream_t st) { return launch_tc<2>(a, st); }

@@ -297,6 +297,36 @@ Tensor mlp_w8a8_quant_forward(Tensor& input, Tensor& gate_weight, Tensor& up_wei
                    B200MOE_ACT_W8A8);
 }
 
+// my_ops/MmW8A16Dq.cpp:185-229: output[M,N] = input[M,K] . dequant(weight [N,K], scale)^T.  Runs on the FP8 tensor
+// cores (activations quantised per row per 128 columns), like the expert GEMMs.
+Tensor mm_w8a16_dq_forward(Tensor& input, Tensor& weight, Tensor& scale, Tensor& output, int64_t blocksize) {
+  check_cuda_contig(input, "input");
+  check_cuda_contig(weight, "weight");
+  check_cuda_contig(scale, "scale");
+  check_cuda_contig(output, "output");
+  TORCH_CHECK(blocksize == 128, "blocksize must be 128");
+  TORCH_CHECK(input.dim() == 2 && input.scalar_type() == kBFloat16, "input must be bf16 [M,K]");
+  TORCH_CHECK(weight.dim() == 2 && weight.scalar_type() == kFloat8_e4m3fn && weight.size(1) == input.size(1),
+              "weight must be float8_e4m3fn [N,K]");
+  const int64_t M = input.size(0), K = input.size(1), N = weight.size(0);
+  TORCH_CHECK(output.scalar_type() == kBFloat16 && output.dim() == 2 && output.size(0) == M && output.size(1) == N,
+              "output must be bf16 [M,N]");
+  TORCH_CHECK(scale.dim() == 2 && scale.size(0) == (N + 127) / 128 && scale.size(1) == (K + 127) / 128,
+              "scale must be [ceil(N/128), ceil(K/128)]");
+  c10::cuda::CUDAGuard guard(input.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  const int sdt = scale_dtype_of(scale);
+  const size_t need = b200moe_linear_workspace_bytes(M, K, N, sdt);
+  TORCH_CHECK(need > 0 || M == 0, "mm_w8a16_dq_forward: unsupported sizes (K % 128 == 0 and N % 64 == 0 required)");
+  Tensor ws = workspace_for(input.device(), st, need);
+  void* wsp = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 255) & ~uintptr_t(255));
+  const size_t ws_bytes = (size_t)ws.numel() - (reinterpret_cast<char*>(wsp) - reinterpret_cast<char*>(ws.data_ptr()));
+  check_rc(b200moe_linear_w8(output.data_ptr(), input.data_ptr(), weight.data_ptr(), scale.data_ptr(), sdt, M, K, N,
+                             wsp, ws_bytes, nullptr, st),
+           "b200moe_linear_w8");
+  return output;
+}
+
 TORCH_LIBRARY(my_ops, m) {
   m.def("fused_moe_grouped_topk", fused_moe_grouped_topk);
   m.def("fused_moe_fused_experts", fused_moe_fused_experts);
@@ -304,6 +334,7 @@ TORCH_LIBRARY(my_ops, m) {
   m.def("noaux_tc_topk", noaux_tc_topk);
   m.def("mlp_w8a16_dq_forward", mlp_w8a16_dq_forward);
   m.def("mlp_w8a8_quant_forward", mlp_w8a8_quant_forward);
+  m.def("mm_w8a16_dq_forward", mm_w8a16_dq_forward);
 }
 
 }  // namespace at

@@ -200,6 +200,26 @@ def grouped_mlp(y, xq, xs_t, expert_offsets, wg, wu, wd, sg, su, sd, R, row_map=
     return y
 
 
+def linear_w8(x, w, scale, out=None, workspace=None, status=None):
+    """out[M,N] = x[M,K] . dequant(w [N,K] e4m3, scale [ceil(N/128), K/128])^T on the FP8 tensor cores (activations
+    quantised 1x128 on the fly).  Reference op: my_ops.mm_w8a16_dq_forward (my_ops/MmW8A16Dq.cpp:185-229)."""
+    _chk(x, "x", torch.bfloat16)
+    _chk(w, "w")
+    _chk(scale, "scale")
+    M, K = x.shape
+    N = w.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    need = L.lib().b200moe_linear_workspace_bytes(M, K, N, _DT[scale.dtype])
+    if workspace is None:
+        workspace = torch.empty(need + 256, dtype=torch.uint8, device=x.device)
+    base = (workspace.data_ptr() + 255) // 256 * 256
+    avail = workspace.numel() - (base - workspace.data_ptr())
+    L.check(L.lib().b200moe_linear_w8(_ptr(out), _ptr(x), _ptr(w), _ptr(scale), _DT[scale.dtype], M, K, N,
+                                      ctypes.c_void_p(base), avail, _ptr(status), _stream()), "b200moe_linear_w8")
+    return out
+
+
 def ep_packed_row_bytes(H):
     return L.lib().b200moe_ep_packed_row_bytes(H)
 
