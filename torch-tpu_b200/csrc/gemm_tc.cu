@@ -412,7 +412,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
       // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
       const float* const S0 = reinterpret_cast<const float*>(a.s0);
-      const float* const S1 = GEMM2 ? S0 : reinterpret_cast<const float*>(a.s1);
+      const float* const S1 = (GEMM2 || DENSE) ? S0 : reinterpret_cast<const float*>(a.s1);  // one scale tensor
       const int sstep = GEMM2 ? nH : 1;
       const int nIs = (a.I + kBlock - 1) / kBlock;  // scale rows of one expert (= nI unless a linear layer's N % 128 != 0)
       const int64_t w0i = (GEMM2   ? (int64_t)e * nI * nH + 2 * nt
