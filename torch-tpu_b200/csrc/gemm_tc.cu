@@ -530,6 +530,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // tile is turned through shared memory (16-byte chunks, XOR-swizzled by row so that neither side has bank
         // conflicts) and a warp stores one row's 256 contiguous bytes per instruction.
         const int wepi = warp - 4;
+        constexpr int ROWS_PER_WARP = 128 / (4 * TC_CG);
+        // destination of the warp's rows, fetched once and in parallel (lane l: row l of the warp's share); walking
+        // tag -> base pointer -> store row by row would put two dependent loads in front of every store
+        int my_tag = 0;
+        unsigned long long my_base = 0;
+        if (lane < ROWS_PER_WARP && row0 + wepi * ROWS_PER_WARP + lane < row_end) {
+          my_tag = a.row_src[row0 + wepi * ROWS_PER_WARP + lane];
+          my_base = a.out_tbl[my_tag >> 24];
+        }
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int col0 = nt * 256 + j * 128;
@@ -549,12 +558,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
           const uint2* st8 = reinterpret_cast<const uint2*>(sh->ostage);
-          constexpr int ROWS_PER_WARP = 128 / (4 * TC_CG);
           for (int rr = 0; rr < ROWS_PER_WARP; ++rr) {
             const int r = wepi * ROWS_PER_WARP + rr;
             if (row0 + r >= row_end) break;  // uniform: rows of a tile are a prefix
-            const int tag = a.row_src[row0 + r];
-            __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(a.out_tbl[tag >> 24]);
+            const int tag = __shfl_sync(0xffffffffu, my_tag, rr);
+            __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, my_base, rr));
             const uint2 v = st8[(r * 16 + ((lane >> 1) ^ (r & 15))) * 2 + (lane & 1)];
             *reinterpret_cast<uint2*>(obase + (int64_t)(tag & 0xFFFFFF) * a.H + col0 + lane * 4) = v;
           }
