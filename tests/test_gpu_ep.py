@@ -124,3 +124,34 @@ def test_ep_plan_tiles_every_destination_buffer():
                 assert dst[r, e] == pos, (d, le, r)
                 pos += cnt[r, e]
         assert pos == rcv[d, El]
+
+
+def test_peer_flag_wait_runs_out_and_reports():
+    """Failure detection without a fault: a 2-rank flag barrier whose peer never announces itself (its flag word is a
+    piece of this process's own memory that nothing sets).  The kernel gives up after its time limit, raises status
+    bit 2 (value 4) and returns; the context stays usable."""
+    import ctypes
+    import time
+    sys.path.insert(0, ROOT)
+    import torch_tpu_b200  # noqa: F401
+    from torch_tpu_b200 import lib as L
+    lib = L.lib()
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")            # [0:8] mine, [32:40] the absent peer's
+    table = torch.tensor([flags.data_ptr(), flags.data_ptr() + 128], dtype=torch.int64, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    t0 = time.time()
+    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(1),
+                                    ctypes.c_void_p(status.data_ptr()), st), "b200moe_p2p_barrier")
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert int(status.item()) == L.STATUS_PEER_TIMEOUT
+    assert 1.0 < waited < 10.0, waited
+    assert int(flags[0].item()) == 1 and int(flags[32].item()) == 1      # both announcements were made
+    # the same barrier completes at once when the peer's word is there
+    flags[1] = 2
+    status.zero_()
+    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(2),
+                                    ctypes.c_void_p(status.data_ptr()), st), "b200moe_p2p_barrier")
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
