@@ -144,43 +144,47 @@ __global__ void gather_scatter_index_kernel(int32_t* __restrict__ gather_index,
 }
 
 // ---- row gather + 1x128 e4m3 quantisation -------------------------------------------------------
-// One warp per (output row, 256-column chunk): a lane owns 8 consecutive bf16 (one 16-byte load), 16 lanes own one
-// 128-column group.  The groups of a row are independent, so they are spread over warps instead of walked by one:
-// at decode sizes (a handful of rows) the kernel is then one load-and-store deep instead of H/256.
+// A warp owns `cpw` consecutive 256-column chunks of one output row: a lane owns 8 consecutive bf16 (one 16-byte
+// load), 16 lanes own one 128-column group.  The groups of a row are independent, so with few rows (decode sizes)
+// they are spread over warps (cpw = 1: the kernel is one load-and-store deep instead of H/256); with many rows one
+// warp walks a whole row (fewer blocks, the row's gather index read once).
 __global__ void __launch_bounds__(256)
 quant_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ s_t, int64_t ld,
                   const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ row_map, int div,
-                  int64_t rows, int H, int chunks) {
+                  int64_t rows, int H, int cpw, int warps_per_row) {
   const int lane = threadIdx.x & 31;
   const int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int64_t r = w / chunks;
+  const int64_t r = w / warps_per_row;
   if (r >= rows) return;
-  const int c = (int)(w - r * chunks) * 256 + lane * 8;
+  const int c_begin = (int)(w - r * warps_per_row) * cpw * 256;
   const int64_t src = row_map ? (int64_t)(row_map[r] / div) : r;
   const __nv_bfloat16* xr = x + src * H;
-  float v[8];
-  float amax = 0.f;
-  if (c < H) {
-    uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
-    const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  for (int c0 = c_begin; c0 < c_begin + cpw * 256 && c0 < H; c0 += 256) {
+    const int c = c0 + lane * 8;
+    float v[8];
+    float amax = 0.f;
+    if (c < H) {
+      uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __bfloat1622float2(b2[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(b2[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
     }
-  }
 #pragma unroll
-  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  if (c < H) {
-    amax = fmaxf(amax, kAmaxFloor);
-    const float inv = kFp8Max / amax;
-    uint2 out;
-    out.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-    out.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-    *reinterpret_cast<uint2*>(q + r * H + c) = out;
-    if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld + r] = amax / kFp8Max;
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (c < H) {
+      amax = fmaxf(amax, kAmaxFloor);
+      const float inv = kFp8Max / amax;
+      uint2 out;
+      out.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+      out.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+      *reinterpret_cast<uint2*>(q + r * H + c) = out;
+      if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld + r] = amax / kFp8Max;
+    }
   }
 }
 
@@ -236,8 +240,10 @@ extern "C" int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void
   if (!moe_aligned16(x) || !moe_aligned16(q)) return B200MOE_EALIGN;
   if (rows == 0) return B200MOE_OK;
   const int chunks = (int)((H + 255) / 256);
-  quant_rows_kernel<<<(unsigned)((rows * chunks + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
-      q, s_t, ld, reinterpret_cast<const __nv_bfloat16*>(x), row_map, (int)div, rows, (int)H, chunks);
+  const int cpw = rows >= 2048 ? chunks : 1;
+  const int warps_per_row = (chunks + cpw - 1) / cpw;
+  quant_rows_kernel<<<(unsigned)((rows * warps_per_row + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      q, s_t, ld, reinterpret_cast<const __nv_bfloat16*>(x), row_map, (int)div, rows, (int)H, cpw, warps_per_row);
   return moe_launch_status();
 }
 
