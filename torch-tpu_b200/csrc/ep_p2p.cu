@@ -117,12 +117,16 @@ __global__ void __launch_bounds__(256)
 ep_dispatch_kernel(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_t* src_tbl,
                    const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ sorted_pair,
                    const int32_t* __restrict__ ids, const int32_t* __restrict__ offsets,
-                   const int32_t* __restrict__ dst_row0, int k, int El, int64_t P, int H, int64_t cap, int rank,
-                   int32_t* status) {
+                   const int32_t* __restrict__ dst_row0, int k, int El, int N, int64_t P, int H, int64_t cap,
+                   int rank, int32_t* status) {
   __shared__ float sc[8][64];
   const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-  const int64_t p = (int64_t)blockIdx.x * 8 + wib;
-  if (p < P) {
+  const int64_t w = (int64_t)blockIdx.x * 8 + wib;
+  // Rows are sorted by destination rank.  Every rank starts with the rows for its right-hand neighbour and wraps
+  // around, so that at any moment the N senders aim at N different receivers instead of all at rank 0 first.
+  const int64_t start = offsets[((rank + 1) % N) * El];
+  const int64_t p = w + start < P ? w + start : w + start - P;
+  if (w < P) {
     const int pair = sorted_pair[p];
     const int e = ids[pair];
     const int d = e / El;
@@ -266,7 +270,7 @@ extern "C" int b200moe_ep_dispatch(const uint64_t* xq_tbl, const uint64_t* xs_tb
   if (P == 0) return B200MOE_OK;
   ep_dispatch_kernel<<<(unsigned)((P + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
       xq_tbl, xs_tbl, src_tbl, reinterpret_cast<const __nv_bfloat16*>(x), sorted_pair, ids, expert_offsets, dst_row0,
-      (int)k, (int)(E / N), P, (int)H, capacity, (int)rank, status);
+      (int)k, (int)(E / N), (int)N, P, (int)H, capacity, (int)rank, status);
   return moe_launch_status();
 }
 
