@@ -42,6 +42,20 @@ def test_host_side_rejections_need_no_gpu(m):
     assert l.b200moe_quant_rows(one, one, 128, one, null, 1, 4, 100, null) == m.lib.ESHAPE
     assert l.b200moe_combine(one, one, one, 0, null, 4, 2, 12, null) == m.lib.ESHAPE
     assert l.b200moe_combine(ctypes.c_void_p(8), one, one, 0, null, 4, 2, 16, null) == m.lib.EALIGN
+    # dense linear layer: K must be a multiple of 128, N of 64; an empty batch is fine without any pointer
+    assert l.b200moe_linear_w8(one, one, one, one, 0, 4, 100, 128, one, 1 << 20, null, null) == m.lib.ESHAPE
+    assert l.b200moe_linear_w8(one, one, one, one, 0, 4, 128, 100, one, 1 << 20, null, null) == m.lib.ESHAPE
+    assert l.b200moe_linear_w8(null, null, null, null, 0, 0, 128, 128, null, 0, null, null) == m.lib.OK
+    assert l.b200moe_linear_w8(null, one, one, one, 0, 4, 128, 128, one, 1 << 20, null, null) == m.lib.EINVAL
+    assert l.b200moe_linear_workspace_bytes(4, 100, 128, 0) == 0
+    assert l.b200moe_linear_workspace_bytes(32, 7168, 576, 1) >= 128 * 7168 + 56 * 128 * 4 + 5 * 56 * 4
+    # peer-memory expert parallelism: at most 8 ranks, the rank inside the group, experts divisible by ranks
+    assert l.b200moe_ep_plan(one, one, one, 256, 9, 0, null) == m.lib.EINVAL
+    assert l.b200moe_ep_plan(one, one, one, 256, 8, 8, null) == m.lib.EINVAL
+    assert l.b200moe_ep_plan(one, one, one, 250, 8, 0, null) == m.lib.ESHAPE
+    assert l.b200moe_p2p_barrier(null, 2, 0, 1, null, null) == m.lib.EINVAL
+    assert l.b200moe_ep_dispatch(one, one, one, one, one, one, one, one, 4, 2, 100, 8, 2, 0, 64, null, null) == m.lib.ESHAPE
+    assert l.b200moe_ep_transpose_scales(one, 64, one, one, 256, 128, null) == m.lib.EINVAL   # ld < capacity
 
 
 def test_workspace_bytes(m):
