@@ -6,7 +6,10 @@
 //   gemm1  h = SiLU(x Wg^T) * (x Wu^T)  per expert, then per-row 1x128 e4m3 requantisation
 //          (stands in for the gate/up part of my_ops/fusedMoE.pl:217-259)
 //   gemm2  y = h Wd                      per expert, rows scattered to their (token,slot) position
-//          (my_ops/fusedMoE.pl:264-269 + scatter_store :55-96)
+//          (my_ops/fusedMoE.pl:264-269 + scatter_store :55-96); with a peer table the rows go straight to
+//          the rank that owns the token (expert parallelism over peer memory: plain peer stores, a warp
+//          stores 256 contiguous bytes of one row after the half tile was turned through shared memory)
+//   linear out = x W^T with W [N,K]      one "expert", no activation, bf16 rows out (my_ops/MmW8A16Dq.cpp:185-229)
 //
 // One persistent CTA per SM, 12 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and TMEM
 // owner, warps 2-3 idle (they only give their registers away), warps 4..11 = epilogue (TMEM lane quarter =
