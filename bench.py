@@ -288,7 +288,16 @@ def main():
 
     if world > 1:
         from torch_tpu_b200.ep import build_ep_layer
-        layer = build_ep_layer(wl, T, dev, rank, world, seed=0, transport=args.ep)
+        try:
+            layer = build_ep_layer(wl, T, dev, rank, world, seed=0, transport=args.ep)
+        except RuntimeError as exc:
+            # peer memory cannot be mapped on this machine (the set-up fails on every rank together): run the
+            # all-to-all exchange instead and say so in the line
+            if args.ep != "p2p" or "peer memory" not in str(exc):
+                raise
+            sys.stderr.write(f"bench: {exc}; using the NCCL all-to-all exchange\n")
+            args.ep = "nccl"
+            layer = build_ep_layer(wl, T, dev, rank, world, seed=0, transport="nccl")
     else:
         layer = build_layer(wl, T_max, dev, seed=0)
 

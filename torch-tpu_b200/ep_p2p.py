@@ -47,14 +47,31 @@ class PeerArena:
         handles = [None] * self.N
         dist.all_gather_object(handles, bytes(h.raw), group=group)
         self.peer_base, self._imported = [], []
+        failed = 0
         for r, hb in enumerate(handles):
             if r == self.rank:
                 self.peer_base.append(self.base)
                 continue
             q = ctypes.c_void_p()
-            L.check(lib.b200moe_p2p_import(ctypes.byref(q), hb), "b200moe_p2p_import")
+            rc = lib.b200moe_p2p_import(ctypes.byref(q), hb)
+            if rc != 0:
+                failed = rc
+                break
             self.peer_base.append(q.value)
             self._imported.append(q.value)
+        # every rank learns whether every mapping exists before anyone goes on (a rank that raised alone would
+        # leave the others waiting for it)
+        flag = torch.tensor([1 if failed else 0], dtype=torch.int32, device=self.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()):
+            for q in self._imported:
+                lib.b200moe_p2p_release(ctypes.c_void_p(q))
+            self._imported = []
+            dist.barrier(group=group)
+            lib.b200moe_p2p_free(ctypes.c_void_p(self.base))
+            self.base = None
+            raise RuntimeError("peer memory could not be mapped on every rank"
+                               + (f" (this rank: {L.error_string(failed)})" if failed else ""))
         self._whole = torch.as_tensor(_RawCuda(self.base, self.nbytes), device=self.device)
         self._tables = {name: torch.tensor([b + o for b in self.peer_base], dtype=torch.int64, device=self.device)
                         for name, (o, _) in self.offsets.items()}
