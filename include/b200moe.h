@@ -225,7 +225,9 @@ int b200moe_linear_w8(void* out, const void* x, const void* w, const void* scale
  * barrier -> combine;
  * all data movement between GPUs is plain peer stores issued by those kernels, and the only waits are flag
  * barriers with a time limit (status bit 2).  `epoch` must grow by one with every barrier (exchange_counts
- * contains one) and take the same values on every rank.
+ * contains one) and take the same values on every rank.  Alternatively pass `epoch_counter`, a device word (zero
+ * at start, one per rank): the barrier then uses counter + 1 and advances the counter itself, so the launches carry
+ * no per-call value and a whole layer call can be captured into a CUDA graph and replayed.
  *
  * Buffers of one rank, for capacity C rows (C >= the most rows the rank can receive, e.g. N*T*k):
  *   flags   uint32 [8]            zero at start            cnt    int32 [N][E]
@@ -237,12 +239,13 @@ int b200moe_p2p_free(void* ptr);
 int b200moe_p2p_export(unsigned char* handle64, void* ptr);      /* 64-byte handle another process can import */
 int b200moe_p2p_import(void** ptr, const unsigned char* handle64);
 int b200moe_p2p_release(void* ptr);                              /* unmap an imported buffer */
-int b200moe_p2p_barrier(const uint64_t* flag_tbl, int64_t N, int64_t rank, uint32_t epoch, int32_t* status,
-                        void* stream);
+int b200moe_p2p_barrier(const uint64_t* flag_tbl, int64_t N, int64_t rank, uint32_t epoch,
+                        uint32_t* epoch_counter, int32_t* status, void* stream);
 /* expert_offsets [E+1] of the rank's own permutation over GLOBAL expert ids -> row `rank` of every peer's cnt;
  * returns after a barrier, so every rank's cnt is complete for the kernels that follow on the stream */
 int b200moe_ep_exchange_counts(const uint64_t* cnt_tbl, const uint64_t* flag_tbl, const int32_t* expert_offsets,
-                               int64_t E, int64_t N, int64_t rank, uint32_t epoch, int32_t* status, void* stream);
+                               int64_t E, int64_t N, int64_t rank, uint32_t epoch, uint32_t* epoch_counter,
+                               int32_t* status, void* stream);
 /* dst_row0 [E]: first row, in the destination's buffers, of this rank's rows of global expert e;
  * recv_offsets [E/N + 1]: expert_offsets of the rows this rank receives (local experts) */
 int b200moe_ep_plan(int32_t* dst_row0, int32_t* recv_offsets, const int32_t* cnt, int64_t E, int64_t N,

@@ -53,7 +53,7 @@ def test_host_side_rejections_need_no_gpu(m):
     assert l.b200moe_ep_plan(one, one, one, 256, 9, 0, null) == m.lib.EINVAL
     assert l.b200moe_ep_plan(one, one, one, 256, 8, 8, null) == m.lib.EINVAL
     assert l.b200moe_ep_plan(one, one, one, 250, 8, 0, null) == m.lib.ESHAPE
-    assert l.b200moe_p2p_barrier(null, 2, 0, 1, null, null) == m.lib.EINVAL
+    assert l.b200moe_p2p_barrier(null, 2, 0, 1, null, null, null) == m.lib.EINVAL
     assert l.b200moe_ep_dispatch(one, one, one, one, one, one, one, one, 4, 2, 100, 8, 2, 0, 64, null, null) == m.lib.ESHAPE
     assert l.b200moe_ep_transpose_scales(one, 64, one, one, 256, 128, null) == m.lib.EINVAL   # ld < capacity
 

@@ -50,8 +50,14 @@ def _run_rank(rank, world, port, q, mode):
             from torch_tpu_b200.ep_p2p import P2PFusedMoE
             ep = P2PFusedMoE(layer, E, max_tokens=256)
             ep(x[:40].to(dev))             # a first call of another size: epochs and buffers are reused after it
-            y = ep(x.to(dev))
+            y = ep(x.to(dev)).clone()
             torch.cuda.synchronize()
+            assert int(ep.status.item()) == 0, int(ep.status.item())
+            # the same call captured into a CUDA graph (device-side epochs, no allocation) and replayed twice
+            for _ in range(2):
+                yg = ep.forward_graph(x.to(dev))
+                torch.cuda.synchronize()
+                assert torch.equal(yg, y)
             assert int(ep.status.item()) == 0, int(ep.status.item())
             ep.close()
         else:
@@ -141,7 +147,7 @@ def test_peer_flag_wait_runs_out_and_reports():
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     t0 = time.time()
-    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(1),
+    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(1), None,
                                     ctypes.c_void_p(status.data_ptr()), st), "b200moe_p2p_barrier")
     torch.cuda.synchronize()
     waited = time.time() - t0
@@ -151,7 +157,7 @@ def test_peer_flag_wait_runs_out_and_reports():
     # the same barrier completes at once when the peer's word is there
     flags[1] = 2
     status.zero_()
-    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(2),
+    L.check(lib.b200moe_p2p_barrier(ctypes.c_void_p(table.data_ptr()), 2, 0, ctypes.c_uint32(2), None,
                                     ctypes.c_void_p(status.data_ptr()), st), "b200moe_p2p_barrier")
     torch.cuda.synchronize()
     assert int(status.item()) == 0

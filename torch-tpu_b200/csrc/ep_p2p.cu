@@ -43,9 +43,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
   return t;
 }
 
-// lanes 0..N-1 of the calling warp: announce `epoch` to peer `lane`, then wait for peer `lane`'s announcement
-__device__ void flag_barrier(const uint64_t* flag_tbl, int N, int rank, uint32_t epoch, int32_t* status) {
+// lanes 0..N-1 of the calling warp: announce `epoch` to peer `lane`, then wait for peer `lane`'s announcement.
+// With a device-side counter the epoch is counter + 1 and the counter is advanced afterwards: the launch then
+// carries no per-call value and can be replayed from a CUDA graph (every rank replays the same sequence).
+__device__ void flag_barrier(const uint64_t* flag_tbl, int N, int rank, uint32_t epoch, uint32_t* counter,
+                             int32_t* status) {
   const int r = threadIdx.x;
+  if (counter) {
+    epoch = *counter + 1;
+    __syncwarp();
+    if (r == 0) *counter = epoch;
+  }
   if (r < N) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t*>(flag_tbl[r]) + rank, epoch);
@@ -64,21 +72,22 @@ __device__ void flag_barrier(const uint64_t* flag_tbl, int N, int rank, uint32_t
   }
 }
 
-__global__ void p2p_barrier_kernel(const uint64_t* flag_tbl, int N, int rank, uint32_t epoch, int32_t* status) {
-  flag_barrier(flag_tbl, N, rank, epoch, status);
+__global__ void p2p_barrier_kernel(const uint64_t* flag_tbl, int N, int rank, uint32_t epoch, uint32_t* counter,
+                                   int32_t* status) {
+  flag_barrier(flag_tbl, N, rank, epoch, counter, status);
 }
 
 // counts of my rows per GLOBAL expert -> row `rank` of every peer's count matrix [N][E]; then a barrier
 __global__ void ep_exchange_counts_kernel(const uint64_t* cnt_tbl, const uint64_t* flag_tbl,
                                           const int32_t* __restrict__ offsets, int E, int N, int rank,
-                                          uint32_t epoch, int32_t* status) {
+                                          uint32_t epoch, uint32_t* counter, int32_t* status) {
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     const int32_t c = offsets[e + 1] - offsets[e];
     for (int d = 0; d < N; ++d) reinterpret_cast<int32_t*>(cnt_tbl[d])[rank * E + e] = c;
   }
   __threadfence_system();
   __syncthreads();
-  flag_barrier(flag_tbl, N, rank, epoch, status);
+  if (threadIdx.x < 32) flag_barrier(flag_tbl, N, rank, epoch, counter, status);
 }
 
 // From the full count matrix cnt[N][E] (identical on every rank after the exchange):
@@ -227,22 +236,22 @@ extern "C" int b200moe_p2p_release(void* ptr) { return ptr ? (int)cudaIpcCloseMe
 
 // ---- steps of the layer ------------------------------------------------------------------------------
 extern "C" int b200moe_p2p_barrier(const uint64_t* flag_tbl, int64_t N, int64_t rank, uint32_t epoch,
-                                   int32_t* status, void* stream) {
+                                   uint32_t* epoch_counter, int32_t* status, void* stream) {
   int rc = check_table_args(flag_tbl, N, rank);
   if (rc) return rc;
-  p2p_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flag_tbl, (int)N, (int)rank, epoch, status);
+  p2p_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flag_tbl, (int)N, (int)rank, epoch, epoch_counter, status);
   return moe_launch_status();
 }
 
 extern "C" int b200moe_ep_exchange_counts(const uint64_t* cnt_tbl, const uint64_t* flag_tbl,
                                           const int32_t* expert_offsets, int64_t E, int64_t N, int64_t rank,
-                                          uint32_t epoch, int32_t* status, void* stream) {
+                                          uint32_t epoch, uint32_t* epoch_counter, int32_t* status, void* stream) {
   int rc = check_table_args(flag_tbl, N, rank);
   if (rc) return rc;
   MOE_CHECK_ARG(cnt_tbl && expert_offsets && E > 0);
   MOE_CHECK_SHAPE(E <= 1024 && E % N == 0);
   ep_exchange_counts_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(cnt_tbl, flag_tbl, expert_offsets, (int)E, (int)N,
-                                                                 (int)rank, epoch, status);
+                                                                 (int)rank, epoch, epoch_counter, status);
   return moe_launch_status();
 }
 

@@ -136,6 +136,8 @@ class P2PFusedMoE:
         self.workspace = torch.empty(need + 256, dtype=torch.uint8, device=self.dev)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self.epoch = 0
+        self.epoch_dev = None      # device-side epoch counter: set by enable_graphs(), see there
+        self._static = None        # buffers of the allocation-free (graph-capturable) form of forward()
         self.phase_events = None   # set to [] to have forward() record (name, event) after every phase
 
     def _next_epoch(self):
@@ -157,10 +159,16 @@ class P2PFusedMoE:
         p, st = ops._ptr, ops._stream
         self._mark("start")
         ids, w = layer.route(x)                                    # ids over GLOBAL experts
-        sorted_pair, offsets = ops.permute(ids, E, status=self.status)
+        if self._static is None:
+            sorted_pair, offsets = ops.permute(ids, E, status=self.status)
+        else:                                                      # graph mode: nothing is allocated per call
+            sorted_pair, offsets = self._static["sorted_pair"][:T * self.k], self._static["offsets"]
+            L.check(lib.b200moe_permute(p(sorted_pair), p(offsets), p(ids), T, self.k, E, p(self._static["scratch"]),
+                                        p(self.status), st()), "b200moe_permute")
         self._mark("route+permute")
         L.check(lib.b200moe_ep_exchange_counts(p(a.table("cnt")), p(a.table("flags")), p(offsets), E, N, rank,
-                                               self._next_epoch(), p(self.status), st()), "b200moe_ep_exchange_counts")
+                                               self._next_epoch(), p(self.epoch_dev), p(self.status), st()),
+                "b200moe_ep_exchange_counts")
         L.check(lib.b200moe_ep_plan(p(self.dst_row0), p(self.recv_offsets), p(self.cnt), E, N, rank, st()),
                 "b200moe_ep_plan")
         self._mark("counts+plan")
@@ -168,8 +176,8 @@ class P2PFusedMoE:
                                         p(sorted_pair), p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank,
                                         self.cap, p(self.status), st()), "b200moe_ep_dispatch")
         self._mark("dispatch")
-        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
-                "b200moe_p2p_barrier")
+        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
+                                        p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier")
         L.check(lib.b200moe_ep_transpose_scales(p(self.xs), self.ld, p(self.xs_rows), p(self.recv_offsets[self.El:]),
                                                 H, self.cap, st()), "b200moe_ep_transpose_scales")
@@ -184,18 +192,73 @@ class P2PFusedMoE:
         self._mark("grouped_mlp")
         add = None
         if layer.shared is not None:                               # local work between the two barriers
-            out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
-            ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
+            if self._static is None:
+                out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
+                ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
+            else:
+                out1 = self._static["shared_out"][:T]
+                ops.experts(out1, x, *layer.shared, self._static["zero_ids"][:T],
+                            workspace=self._static["shared_ws"])
             add = out1.view(T, H)
             self._mark("shared")
-        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.status), st()),
-                "b200moe_p2p_barrier")
+        L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
+                                        p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier2")
-        out = ops.combine(self.y[:T], w, add=add)
+        out = ops.combine(self.y[:T], w, add=add, out=None if self._static is None else self._static["out"][:T])
         self._mark("combine")
         return out
 
     __call__ = forward
+
+    def enable_graphs(self):
+        """Switch to the allocation-free form of forward(): every buffer is made once here, and the barriers count
+        their epochs in a device word instead of taking them from the host, so that a call holds no per-call value
+        and can be captured into a CUDA graph.  Every rank of the group must switch at the same point of its call
+        sequence (the device counter starts from the host's current epoch)."""
+        if self._static is not None:
+            return
+        dev, T, k, H, E = self.dev, self.max_tokens, self.k, self.H, self.E
+        st = dict(sorted_pair=torch.empty(T * k, dtype=torch.int32, device=dev),
+                  offsets=torch.empty(E + 1, dtype=torch.int32, device=dev),
+                  scratch=torch.empty(max(1, L.lib().b200moe_permute_scratch_ints(T * k, E)), dtype=torch.int32,
+                                      device=dev),
+                  out=torch.empty(T, H, dtype=torch.bfloat16, device=dev),
+                  x=torch.empty(T, H, dtype=torch.bfloat16, device=dev))
+        if self.layer.shared is not None:
+            Is = self.layer.shared[0].shape[-2]
+            d = ops.make_desc(T, H, Is, 1, 1, out_mode=L.OUT_PER_SLOT, scale_dtype=self.layer.shared[3].dtype)
+            st.update(shared_out=torch.empty(T, 1, H, dtype=torch.bfloat16, device=dev),
+                      zero_ids=torch.zeros(T, 1, dtype=torch.int32, device=dev),
+                      shared_ws=torch.empty(ops.experts_workspace_bytes(d) + 256, dtype=torch.uint8, device=dev))
+        self.epoch_dev = torch.tensor([self.epoch], dtype=torch.int32, device=dev)
+        self._static, self._graphs = st, {}
+
+    def capture(self, T: int):
+        """Capture forward() for exactly T tokens per rank into a CUDA graph (every rank captures and later replays
+        the same sequence; the flag barriers inside the graph keep the ranks in step)."""
+        self.enable_graphs()
+        x_static = self._static["x"][:T]
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):           # first calls set function attributes: keep them out of the capture
+                self.forward(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y = self.forward(x_static)
+        self._graphs[T] = (g, y)
+        return g
+
+    def forward_graph(self, x):
+        """Replay the graph captured for x.shape[0] tokens (captures it on first use)."""
+        T = x.shape[0]
+        if self._static is None or T not in self._graphs:
+            self.capture(T)
+        g, y = self._graphs[T]
+        self._static["x"][:T].copy_(x, non_blocking=True)
+        g.replay()
+        return y
 
     def forward_host(self, x_host, out_host):
         """Host-buffer entry point, pipelined like FusedMoE.forward_host."""

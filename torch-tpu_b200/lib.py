@@ -67,9 +67,9 @@ SIGNATURES = {
     "b200moe_p2p_export": (c_int, [c_char_p, c_void_p]),
     "b200moe_p2p_import": (c_int, [POINTER(c_void_p), c_char_p]),
     "b200moe_p2p_release": (c_int, [c_void_p]),
-    "b200moe_p2p_barrier": (c_int, [c_void_p, c_int64, c_int64, c_uint32, c_void_p, c_void_p]),
+    "b200moe_p2p_barrier": (c_int, [c_void_p, c_int64, c_int64, c_uint32, c_void_p, c_void_p, c_void_p]),
     "b200moe_ep_exchange_counts": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_uint32, c_void_p,
-                                           c_void_p]),
+                                           c_void_p, c_void_p]),
     "b200moe_ep_plan": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "b200moe_ep_dispatch": (c_int, [c_void_p] * 8 + [c_int64] * 7 + [c_void_p, c_void_p]),
     "b200moe_ep_transpose_scales": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
