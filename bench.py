@@ -37,7 +37,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the dominant kernel (gate/up GEMM) at the headline
 # size, taken from an ncu capture of this very command (profiles/moe_gemm_tc_dram_traffic.md); bench.py cannot run ncu
 # itself, so the figure is carried here and is null for sizes that were not captured.
-NCU_TRAFFIC_BYTES = {("mixtral", 4096): 1295.8e6}
+NCU_TRAFFIC_BYTES = {("mixtral", 4096): 1295.8e6, ("qwen", 8192): 245.3e6}
 
 
 def load_peaks():
