@@ -105,7 +105,7 @@ def algorithmic(wl, T, e_act):
     return flops, wbytes + abytes
 
 
-def build_layer(wl, T_max, dev, seed, first_expert=0, n_local=None):
+def build_layer(wl, T_max, dev, seed, first_expert=0, n_local=None, fused_combine=False):
     import torch
     import torch_tpu_b200
     from torch_tpu_b200 import weights as W
@@ -127,7 +127,8 @@ def build_layer(wl, T_max, dev, seed, first_expert=0, n_local=None):
     shared = W.random_experts(1, wl["H"], wl["shared"], dev, seed=seed + 777) if wl.get("shared") else None
     cfg = MoEConfig(wl["H"], wl["I"], E, wl["k"], wl["score"], wl.get("groups", 1), wl.get("topk_groups", 1), True,
                     wl.get("scale", 1.0), wl.get("shared", 0))
-    layer = FusedMoE(cfg, wr, *w, bias=bias, shared=shared, logit_bias=logit_bias, max_tokens=T_max)
+    layer = FusedMoE(cfg, wr, *w, bias=bias, shared=shared, logit_bias=logit_bias, max_tokens=T_max,
+                     fused_combine=fused_combine)
     return layer
 
 
@@ -353,11 +354,11 @@ def main():
         def only(mask):
             def f():
                 ops.experts(out, xs[0], wg, wu, wd, sg, su, sd, ids, layer.topk_w[:T], shared=layer.shared,
-                            workspace=layer.workspace, reserved=mask)
+                            workspace=layer.workspace, stages=mask)
             return f
         layer.forward(xs[0])
-        ms_g1 = time_steps(only(16 | 64 | 128), args.steps, 3)
-        ms_g2 = time_steps(only(16 | 32 | 128), args.steps, 3)
+        ms_g1 = time_steps(only(L.STAGE_GATE_UP), args.steps, 3)
+        ms_g2 = time_steps(only(L.STAGE_DOWN), args.steps, 3)
         flops, nbytes = algorithmic(wl, T, e_act)
         Is = wl.get("shared", 0)
         f_g1 = 4.0 * T * wl["k"] * wl["H"] * wl["I"] + 4.0 * T * wl["H"] * Is

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 1
+#define B200MOE_ABI_VERSION 2
 
 enum {
   B200MOE_OK = 0,
@@ -42,7 +42,22 @@ enum { B200MOE_SCORE_SOFTMAX = 0, B200MOE_SCORE_SIGMOID = 1 };
 /* output modes of b200moe_experts */
 enum {
   B200MOE_OUT_PER_SLOT = 0, /* out [T,k,H] bf16, un-weighted (what the reference op returns) */
-  B200MOE_OUT_COMBINED = 1  /* out [T,H] bf16 = sum_j w[t,j] * y[t,j,:] (+ shared expert)     */
+  B200MOE_OUT_COMBINED = 1, /* out [T,H] bf16 = sum_j w[t,j] * y[t,j,:] (+ shared expert): per-slot rows go to
+                               the workspace and a second kernel sums them in slot order (bit-reproducible) */
+  B200MOE_OUT_COMBINED_FUSED = 2 /* the same sum formed inside the down GEMM's epilogue: every result row is
+                               multiplied by its routing weight and added (fp32 reductions) into a [T,H]
+                               buffer, then rounded to bf16 once.  No per-slot rows in memory; the order of
+                               the k additions is not fixed, so the last bit may differ from run to run.
+                               Tensor-core path only (elsewhere it behaves like B200MOE_OUT_COMBINED). */
+};
+
+/* stages of b200moe_experts (b200moe_experts_desc.stages) */
+enum {
+  B200MOE_STAGE_PREP = 1,    /* permutation, tile list, activation quantisation, scale conversion */
+  B200MOE_STAGE_GATE_UP = 2, /* gate/up GEMM + SiLU*up (+ requantisation) */
+  B200MOE_STAGE_DOWN = 4,    /* down GEMM + scatter (or fused combine) */
+  B200MOE_STAGE_COMBINE = 8, /* weighted combine / final rounding */
+  B200MOE_STAGE_ALL = 15
 };
 
 /* arithmetic of the expert GEMMs */
@@ -97,7 +112,9 @@ int b200moe_route(int32_t* ids, float* w, void* w_bf16, const float* logits, con
 /* Stable sort of the T*k (token,slot) pairs by expert id: sorted_pair[P] (flat t*k+j, ascending
  * inside an expert), expert_offsets[E+1].  The device twin of phases 1-2 of the reference kernel
  * (my_ops/fusedMoE.pl:624-756).  scratch: int32[b200moe_permute_scratch_ints(P,E)].
- * Ids outside [0,E) are dropped (status bit 0). */
+ * Ids outside [0,E) are dropped (status bit 0): expert_offsets[E] is then smaller than T*k and the tail
+ * sorted_pair[expert_offsets[E] .. T*k) holds -1; every kernel of this library that walks sorted_pair skips
+ * negative entries, and in the per-slot output the rows of dropped pairs are left untouched. */
 size_t b200moe_permute_scratch_ints(int64_t P, int64_t E);
 int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
                     int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream);
@@ -156,8 +173,11 @@ typedef struct {
   int impl;           /* B200MOE_IMPL_* */
   int scale_dtype;    /* B200MOE_F32 | B200MOE_BF16 */
   int w_dtype;        /* dtype of topk_w: B200MOE_F32 | B200MOE_BF16 */
-  int reserved;       /* 0; tests: bits 0-1 / 2-3 force the gate-up / down GEMM to 1 = simple, 2 = tcgen05;
-                         profiling: bits 4..7 skip permute+quantise / gate-up GEMM / down GEMM / combine */
+  int impl_gate_up;   /* B200MOE_IMPL_AUTO = follow `impl`; else the kernel family of the gate/up GEMM alone */
+  int impl_down;      /* the same for the down GEMM (tests A/B one GEMM at a time with these two) */
+  int stages;         /* 0 = the whole call.  Else a mask of B200MOE_STAGE_*: only those stages are enqueued, on
+                         a workspace that a whole call with the same sizes and inputs has filled before (how a
+                         benchmark times one GEMM alone).  Any other bit is rejected. */
 } b200moe_experts_desc;
 
 size_t b200moe_experts_workspace_bytes(const b200moe_experts_desc* d);
@@ -175,9 +195,14 @@ int b200moe_experts(void* out, const void* x, const void* w_gate, const void* w_
 int b200moe_combine(void* out, const void* y, const void* w, int w_dtype, const void* add, int64_t T,
                     int64_t k, int64_t H, void* stream);
 
-/* Same with the rows of y taken through an index: row of pair (t,j) = pos[t*k+j] (pos NULL = t*k+j). */
+/* Same with the rows of y taken through an index: row of pair (t,j) = pos[t*k+j] (pos NULL = t*k+j); a negative
+ * pos entry contributes nothing. */
 int b200moe_combine_indexed(void* out, const void* y, const int32_t* pos, const void* w, int w_dtype,
                             const void* add, int64_t T, int64_t k, int64_t H, void* stream);
+/* Same, and slots whose expert id ids[t*k+j] lies outside [0,E) contribute nothing either (their rows of y were
+ * never written: the permutation drops such pairs).  ids NULL = no such check. */
+int b200moe_combine_masked(void* out, const void* y, const int32_t* pos, const void* w, int w_dtype, const void* add,
+                           const int32_t* ids, int64_t E, int64_t T, int64_t k, int64_t H, void* stream);
 
 /* ---- expert parallelism ------------------------------------------------------------------------------------
  * The reference has no expert-parallel path (its only MoE-adjacent collective is an equal-split all-to-all,
@@ -205,7 +230,7 @@ int b200moe_ep_pack_rows(uint8_t* rows, const void* x, const int32_t* sorted_pai
 int b200moe_ep_unpack_ids(int32_t* eid, const uint8_t* rows, int64_t R, int64_t H, void* stream);
 int b200moe_ep_unpack_rows(uint8_t* xq, float* xs_t, int64_t ld, const uint8_t* rows, const int32_t* order,
                            int64_t R, int64_t H, void* stream);
-/* inv[perm[i]] = i */
+/* inv[perm[i]] = i; entries of perm outside [0,n) are skipped and entries of inv that nothing names are -1 */
 int b200moe_invert_permutation(int32_t* inv, const int32_t* perm, int64_t n, void* stream);
 
 /* ---- FP8 block-scaled linear layer ----------------------------------------------------------------------

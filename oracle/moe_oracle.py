@@ -242,15 +242,23 @@ def expert_mlp_w8a16(x: torch.Tensor, wg, wu, wd_ih, sg, su, sd_ih,
     return F.linear(h, dq2)
 
 
-def experts_w8a16(x, ids, wg, wu, wd, sg, su, sd, dtype: torch.dtype = torch.bfloat16
-                  ) -> torch.Tensor:
+def experts_w8a16(x, ids, wg, wu, wd, sg, su, sd, dtype: torch.dtype = torch.bfloat16,
+                  per_token: bool = False) -> torch.Tensor:
     """oracle-A.  ``out[t,j,:] = expert[ids[t,j]](x[t])`` (``DeepseekMoE.forward``,
-    python/regression/test_llm/test_moe.py:93-98), un-weighted, ``[T,k,H]``.  Rows of one expert
-    are batched through one dequantisation ("hoisted"); the reference dequantises per
-    (token,slot), which changes nothing arithmetically but the cost."""
+    python/regression/test_llm/test_moe.py:93-98), un-weighted, ``[T,k,H]``.  By default the rows
+    of one expert are batched through one dequantisation ("hoisted"); the reference dequantises
+    per (token,slot) and hands the expert the 1-D row ``x[t]``, which changes nothing in the
+    statements but the cost and, possibly, the blocking of the bf16 matrix products (so the last
+    bit of a few elements).  ``per_token=True`` walks the pairs exactly as the reference does."""
     T, k = ids.shape
     H = x.shape[1]
     out = torch.zeros(T, k, H, dtype=dtype)
+    if per_token:
+        for t in range(T):
+            for j in range(k):
+                e = int(ids[t, j])
+                out[t, j, :] = expert_mlp_w8a16(x[t], wg[e], wu[e], wd[e], sg[e], su[e], sd[e], dtype=dtype)
+        return out
     flat = ids.reshape(-1).to(torch.int64)
     for e in torch.unique(flat).tolist():
         pos = torch.nonzero(flat == e).flatten()

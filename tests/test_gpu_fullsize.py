@@ -1,5 +1,7 @@
 """Parity at the benchmark's own sizes (Mixtral-8x7B shape, 4096 tokens; DeepSeek-V3 shape, 2048 tokens with the
-shared expert).  The CPU oracle cannot redo a whole step at these sizes, so:
+shared expert; Qwen3-30B-A3B shape, 8192 tokens with Zipf-skewed routing) and at the decode sizes of the same shapes
+(Mixtral 1 / 32 / 512 tokens, DeepSeek 1 / 64 tokens: the K-split down GEMM, the side-stream shared expert and the
+CUDA-graph replay are what run there).  The CPU oracle cannot redo a whole prefill step, so:
 
   - routing ids and the permutation are checked exactly for ALL tokens (they are cheap on the CPU);
   - size-independent properties are checked on the whole output: the step is bit-reproducible, and the combined
@@ -21,16 +23,53 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DEV = "cuda:0"
 
 
+_LAYERS = {}
+
+
 def _layer(workload, T):
+    """One layer per workload for the whole module (weights of the DeepSeek shape are 11 GB), sized for the
+    workload's largest batch, with the workspace of the fused-combine mode (which covers the other modes)."""
     sys.path.insert(0, ROOT)
     import bench
     wl = bench.WORKLOADS[workload]
-    layer = bench.build_layer(wl, T, DEV, seed=0)
-    x = bench.make_x(T, wl["H"], DEV, seed=100).to(DEV)
+    if workload not in _LAYERS:
+        _LAYERS.clear()                       # one workload's weights on the device at a time
+        torch.cuda.empty_cache()
+        _LAYERS[workload] = bench.build_layer(wl, max(wl["tokens"]), DEV, seed=0, fused_combine=True)
+    layer = _LAYERS[workload]
+    layer.fused_combine = False
+    x = bench.make_x(T, wl["H"], DEV, seed=100 + T).to(DEV)
     return bench, wl, layer, x
 
 
-@pytest.mark.parametrize("workload,T,n_sample", [("mixtral", 4096, 256), ("deepseek", 2048, 32)])
+def _route_oracle(wl, layer, logits):
+    """(tie-free mask, ids, weights) of the oracle on the device's own logits."""
+    k = wl["k"]
+    if wl["score"] == "softmax":
+        if layer.logit_bias is not None:
+            logits = logits + layer.logit_bias.cpu()
+        ok = O.tie_free_rows(torch.softmax(logits, -1), k)
+        wid, ww = O.route_softmax_topk(logits, k)
+    else:
+        bias = layer.bias.cpu()
+        ok = O.tie_free_rows(torch.sigmoid(logits) + bias, k, wl["groups"], wl["topk_groups"])
+        wid, ww = O.route_sigmoid_grouped(logits, bias, wl["groups"], wl["topk_groups"], k, wl["scale"])
+    return ok, wid, ww
+
+
+def _oracle_rows(wl, layer, x, ids, w, idx):
+    """Oracle output of the tokens ``idx`` (only the experts they activate travel to the host)."""
+    E = wl["E"]
+    xs, ids_s, w_s = x[idx.to(DEV)].cpu(), ids.cpu()[idx], w.cpu()[idx]
+    used = torch.unique(ids_s.long())
+    wts = [t[used.to(DEV)].cpu() for t in layer.w]
+    remap = torch.full((E,), -1, dtype=torch.long)
+    remap[used] = torch.arange(len(used))
+    shared = tuple(t[0].cpu() for t in layer.shared) if layer.shared is not None else None
+    return O.moe_layer_w8a8(xs, remap[ids_s.long()].to(torch.int32), tuple(wts), shared=shared, topk_w=w_s)
+
+
+@pytest.mark.parametrize("workload,T,n_sample", [("mixtral", 4096, 256), ("qwen", 8192, 128), ("deepseek", 2048, 32)])
 def test_full_size_step(workload, T, n_sample):
     import torch_tpu_b200  # noqa: F401
     from torch_tpu_b200 import ops
@@ -43,13 +82,7 @@ def test_full_size_step(workload, T, n_sample):
     logits = layer.logits[:T].cpu()
 
     # ---- routing, all tokens: exact on the device's own logits --------------------------------------------------
-    if wl["score"] == "softmax":
-        ok = O.tie_free_rows(torch.softmax(logits, -1), k)
-        wid, ww = O.route_softmax_topk(logits, k)
-    else:
-        bias = layer.bias.cpu()
-        ok = O.tie_free_rows(torch.sigmoid(logits) + bias, k, wl["groups"], wl["topk_groups"])
-        wid, ww = O.route_sigmoid_grouped(logits, bias, wl["groups"], wl["topk_groups"], k, wl["scale"])
+    ok, wid, ww = _route_oracle(wl, layer, logits)
     assert ok.float().mean() > 0.97
     assert torch.equal(ids.cpu()[ok], wid[ok])
     torch.testing.assert_close(w.cpu()[ok], ww[ok], rtol=1e-5, atol=1e-6)
@@ -80,12 +113,42 @@ def test_full_size_step(workload, T, n_sample):
     # ---- expert arithmetic on a seeded subsample ----------------------------------------------------------------
     g = torch.Generator().manual_seed(7)
     idx = torch.randperm(T, generator=g)[:n_sample].sort().values
-    xs, ids_s, w_s = x[idx.to(DEV)].cpu(), ids.cpu()[idx], w.cpu()[idx]
-    used = torch.unique(ids_s.long())
-    wts = [t[used.to(DEV)].cpu() for t in layer.w]                                 # only these experts travel
-    remap = torch.full((E,), -1, dtype=torch.long)
-    remap[used] = torch.arange(len(used))
-    shared = tuple(t[0].cpu() for t in layer.shared) if layer.shared is not None else None
-    want = O.moe_layer_w8a8(xs, remap[ids_s.long()].to(torch.int32), tuple(wts), shared=shared, topk_w=w_s)
+    want = _oracle_rows(wl, layer, x, ids, w, idx)
     met = O.parity_metrics(y[idx.to(DEV)].cpu(), want)
     assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+
+    # ---- the weighted combine fused into the down GEMM's epilogue: same sums, order of the k additions free -------
+    layer.fused_combine = True
+    yf = layer.forward(x).clone()
+    torch.cuda.synchronize()
+    layer.fused_combine = False
+    assert int(layer.status.item()) == 0
+    met = O.parity_metrics(yf[idx.to(DEV)].cpu(), want)
+    assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
+    met = O.parity_metrics(yf, y)
+    assert met["max_rel"] <= 8e-3 and met["cosine"] >= 0.99999, met               # one bf16 rounding per slot apart
+
+
+@pytest.mark.parametrize("workload,T,n_check", [("mixtral", 1, 1), ("mixtral", 32, 32), ("mixtral", 512, 512),
+                                                ("deepseek", 1, 1), ("deepseek", 64, 8)])
+def test_decode_sizes_at_real_shapes(workload, T, n_check):
+    """Decode-size batches of the benchmark shapes, through forward() and through the CUDA-graph replay: routing ids
+    exact for all tokens, outputs against the oracle at the stated tolerance (all tokens; for the DeepSeek shape at
+    64 tokens a seeded sample of 8, whose 64 experts are what still travels to the host in reasonable time)."""
+    import torch_tpu_b200  # noqa: F401
+    bench, wl, layer, x = _layer(workload, T)
+    y = layer.forward(x).clone()
+    torch.cuda.synchronize()
+    assert int(layer.status.item()) == 0
+    ids, w = layer.ids[:T].clone(), layer.topk_w[:T].clone()
+    ok, wid, ww = _route_oracle(wl, layer, layer.logits[:T].cpu())
+    assert torch.equal(ids.cpu()[ok], wid[ok]) and ok.float().mean() > 0.9
+    yg = layer.forward_graph(x).clone()
+    torch.cuda.synchronize()
+    assert int(layer.status.item()) == 0
+    assert torch.equal(layer.ids[:T], ids)
+    idx = torch.randperm(T, generator=torch.Generator().manual_seed(3))[:n_check].sort().values
+    want = _oracle_rows(wl, layer, x, ids, w, idx)
+    for got in (y, yg):
+        met = O.parity_metrics(got[idx.to(DEV)].cpu(), want)
+        assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met

@@ -22,6 +22,7 @@ ep_pack_rows_kernel(uint8_t* __restrict__ rows, const __nv_bfloat16* __restrict_
   const int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (p >= P) return;
   const int pair = sorted_pair[p];
+  if (pair < 0) return;  // position of a dropped pair (id out of range): nothing to pack
   const __nv_bfloat16* xr = x + (int64_t)(pair / k) * H;
   uint8_t* out = rows + p * RB;
   float* sc = reinterpret_cast<float*>(out + H);
@@ -68,7 +69,7 @@ ep_unpack_rows_kernel(uint8_t* __restrict__ xq, float* __restrict__ xs_t, int64_
                       int64_t RB) {
   const int lane = threadIdx.x & 31;
   const int64_t p = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (p >= R) return;
+  if (p >= R || order[p] < 0) return;  // -1: position of a row whose expert id was out of range
   const uint8_t* src = rows + (int64_t)order[p] * RB;
   for (int c = lane * 16; c < H; c += 512)
     *reinterpret_cast<uint4*>(xq + p * H + c) = *reinterpret_cast<const uint4*>(src + c);
@@ -78,7 +79,7 @@ ep_unpack_rows_kernel(uint8_t* __restrict__ xq, float* __restrict__ xs_t, int64_
 
 __global__ void invert_permutation_kernel(int32_t* __restrict__ inv, const int32_t* __restrict__ perm, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < n) inv[perm[i]] = (int32_t)i;
+  if (i < n && perm[i] >= 0 && perm[i] < n) inv[perm[i]] = (int32_t)i;
 }
 
 }  // namespace
@@ -121,6 +122,8 @@ extern "C" int b200moe_ep_unpack_rows(uint8_t* xq, float* xs_t, int64_t ld, cons
 extern "C" int b200moe_invert_permutation(int32_t* inv, const int32_t* perm, int64_t n, void* stream) {
   MOE_CHECK_ARG(inv && perm && n >= 0);
   if (n == 0) return B200MOE_OK;
+  // entries that no perm[i] names (perm carries -1 for dropped pairs) stay -1
+  cudaMemsetAsync(inv, 0xFF, (size_t)n * sizeof(int32_t), (cudaStream_t)stream);
   invert_permutation_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(inv, perm, n);
   return moe_launch_status();
 }

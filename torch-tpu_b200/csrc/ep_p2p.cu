@@ -20,7 +20,7 @@
 // collective is an equal-split all-to-all, torch_tpu/csrc/distributed/c10d/ProcessGroupSCCL.cpp:714-743).
 //
 // Flags: one uint32 per (rank, peer) holding the last epoch that peer announced; epochs only grow, so nothing is
-// ever reset.  A wait gives up after about two seconds and raises status bit 4; the kernel then returns.
+// ever reset.  A wait gives up after about two seconds and raises status bit 2 (value 4); the kernel then returns.
 // Plain peer loads and stores only: no multimem, no multicast.
 #include "common.cuh"
 
@@ -135,8 +135,8 @@ ep_dispatch_kernel(const uint64_t* xq_tbl, const uint64_t* xs_tbl, const uint64_
   // around, so that at any moment the N senders aim at N different receivers instead of all at rank 0 first.
   const int64_t start = offsets[((rank + 1) % N) * El];
   const int64_t p = w + start < P ? w + start : w + start - P;
-  if (w < P) {
-    const int pair = sorted_pair[p];
+  const int pair = w < P ? sorted_pair[p] : -1;  // -1 also marks the position of a dropped pair (id out of range)
+  if (pair >= 0) {
     const int e = ids[pair];
     const int d = e / El;
     const int64_t row = (int64_t)dst_row0[e] + (p - offsets[e]);

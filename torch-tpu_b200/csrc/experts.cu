@@ -23,7 +23,7 @@ int choose_ksplit(int64_t P, int64_t E, int64_t H, int64_t I) {
 }
 
 struct WsLayout {
-  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32, y32, s_y32;
+  size_t offsets, sorted, scratch, mtiles, nmt, xq, xs, hq, hs, y, sc32, s_sc32, y32, s_y32, acc32;
   size_t s_offsets, s_mtiles, s_nmt, s_xq, s_xs, s_hq, s_hs, s_y;
   size_t total;
   int64_t P, ld, lds;
@@ -55,7 +55,10 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   L.xs = take(w8a8 ? nH * (size_t)L.ld * sizeof(float) : 0);
   L.hq = take(w8a8 ? (size_t)P * d.I : (size_t)P * d.I * 2);
   L.hs = take(w8a8 ? nI * (size_t)L.ld * sizeof(float) : 0);
-  L.y = take(d.out_mode == B200MOE_OUT_COMBINED ? (size_t)P * d.H * 2 : 0);
+  // combined output: per-slot rows for the separate combine kernel; the fused combine adds into an fp32 [T,H] buffer
+  // instead (both are laid out, so that one workspace serves either mode of the same sizes)
+  L.y = take(d.out_mode != B200MOE_OUT_PER_SLOT ? (size_t)P * d.H * 2 : 0);
+  L.acc32 = take(d.out_mode == B200MOE_OUT_COMBINED_FUSED && w8a8 ? (size_t)d.T * d.H * sizeof(float) : 0);
   // fp32 partial sums of the K-split down GEMM (decode-size batches only)
   // (sized for min(P, limit) rows whatever P is, so that the workspace size never shrinks when T grows)
   L.y32 = take(w8a8 ? (size_t)(P < kSplitMaxPairs ? P : kSplitMaxPairs) * d.H * sizeof(float) : 0);
@@ -114,7 +117,11 @@ constexpr int64_t kSharedOverlapMaxTokens = 64;
 int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_ARG(d);
   MOE_CHECK_ARG(d->T >= 0 && d->H > 0 && d->I > 0 && d->E > 0 && d->k > 0 && d->I_shared >= 0);
-  MOE_CHECK_ARG(d->out_mode == B200MOE_OUT_PER_SLOT || d->out_mode == B200MOE_OUT_COMBINED);
+  MOE_CHECK_ARG(d->out_mode == B200MOE_OUT_PER_SLOT || d->out_mode == B200MOE_OUT_COMBINED ||
+                d->out_mode == B200MOE_OUT_COMBINED_FUSED);
+  MOE_CHECK_ARG(d->impl_gate_up >= B200MOE_IMPL_AUTO && d->impl_gate_up <= B200MOE_IMPL_TCGEN05);
+  MOE_CHECK_ARG(d->impl_down >= B200MOE_IMPL_AUTO && d->impl_down <= B200MOE_IMPL_TCGEN05);
+  MOE_CHECK_ARG((d->stages & ~B200MOE_STAGE_ALL) == 0);
   MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8 || d->act_mode == B200MOE_ACT_W8A16);
   MOE_CHECK_ARG(d->impl >= B200MOE_IMPL_AUTO && d->impl <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG(d->scale_dtype == B200MOE_F32 || d->scale_dtype == B200MOE_BF16);
@@ -122,7 +129,7 @@ int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_SHAPE(d->H % kBlock == 0 && d->I % kBlock == 0 && d->I_shared % kBlock == 0);
   MOE_CHECK_SHAPE(d->E <= 1024 && d->T * d->k < (1 << 24));
   MOE_CHECK_SHAPE(d->H < (1 << 24) && d->I < (1 << 24) && d->E * d->I < (int64_t(1) << 31));
-  if (d->I_shared > 0) MOE_CHECK_ARG(d->out_mode == B200MOE_OUT_COMBINED);
+  if (d->I_shared > 0) MOE_CHECK_ARG(d->out_mode != B200MOE_OUT_PER_SLOT);
   if (d->impl == B200MOE_IMPL_TCGEN05) MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8);
   return B200MOE_OK;
 }
@@ -145,7 +152,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   if (rc != B200MOE_OK) return rc;
   if (d->T == 0) return B200MOE_OK;  // nothing to do; empty tensors may carry null pointers
   MOE_CHECK_ARG(out && x && w_gate && w_up && w_down && s_gate && s_up && s_down && ids);
-  if (d->out_mode == B200MOE_OUT_COMBINED) MOE_CHECK_ARG(topk_w);
+  if (d->out_mode != B200MOE_OUT_PER_SLOT) MOE_CHECK_ARG(topk_w);
   if (d->I_shared > 0)
     MOE_CHECK_ARG(shared_w_gate && shared_w_up && shared_w_down && shared_s_gate && shared_s_up && shared_s_down);
   if (!moe_aligned16(out) || !moe_aligned16(x) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
@@ -160,21 +167,26 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   const bool w8a8 = d->act_mode == B200MOE_ACT_W8A8;
   const bool use_tc = w8a8 && d->impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
   if (d->impl == B200MOE_IMPL_TCGEN05 && !use_tc) return B200MOE_EDRIVER;
-  const bool combined = d->out_mode == B200MOE_OUT_COMBINED;
-  // per-GEMM override for A/B tests: reserved bits 0-1 (gate/up GEMM) and 2-3 (down GEMM): 1 = simple, 2 = tcgen05
-  const int o1 = d->reserved & 3, o2 = (d->reserved >> 2) & 3;
-  const bool tc1 = w8a8 && moe_tc_available() && (o1 ? o1 == 2 : use_tc);
-  const bool tc2 = w8a8 && moe_tc_available() && (o2 ? o2 == 2 : use_tc);
-  // stage mask for profiling (a stage may be re-run alone on a workspace that a full call has filled):
-  // reserved bit 4 = skip permute/quantise, bit 5 = skip gate-up GEMM, bit 6 = skip down GEMM, bit 7 = skip combine
-  const bool do_prep = !(d->reserved & 16), do_g1 = !(d->reserved & 32), do_g2 = !(d->reserved & 64),
-             do_comb = !(d->reserved & 128);
+  const bool combined = d->out_mode != B200MOE_OUT_PER_SLOT;
+  // per-GEMM kernel family (A/B tests), else the call's
+  const bool tc1 = w8a8 && moe_tc_available() && (d->impl_gate_up ? d->impl_gate_up == B200MOE_IMPL_TCGEN05 : use_tc);
+  const bool tc2 = w8a8 && moe_tc_available() && (d->impl_down ? d->impl_down == B200MOE_IMPL_TCGEN05 : use_tc);
+  // the fused combine lives in the tensor-core down GEMM's epilogue; other paths combine with the separate kernel
+  const bool fused = d->out_mode == B200MOE_OUT_COMBINED_FUSED && tc2;
+  // a stage may be re-run alone on a workspace that a whole call of the same sizes has filled
+  const int stages = d->stages ? d->stages : B200MOE_STAGE_ALL;
+  const bool do_prep = stages & B200MOE_STAGE_PREP, do_g1 = stages & B200MOE_STAGE_GATE_UP,
+             do_g2 = stages & B200MOE_STAGE_DOWN, do_comb = stages & B200MOE_STAGE_COMBINE;
 
   // Decode-size batches with a shared expert: the shared expert runs on a side stream beside the routed experts.
   // The fork is recorded before any routed work is queued, so both passes start together; they share no workspace
   // region.  One call per device at a time may use the side stream (calls on one device are expected to be queued
   // from one host thread).
-  SideStream* side = (d->I_shared > 0 && use_tc && d->T <= kSharedOverlapMaxTokens && d->reserved == 0)
+  // fused combine: the sums of the routed AND the shared expert meet in this buffer, so it is cleared before the
+  // side stream forks off
+  float* acc32 = reinterpret_cast<float*>(ws + L.acc32);
+  if (fused && do_g2) cudaMemsetAsync(acc32, 0, (size_t)d->T * d->H * sizeof(float), st);
+  SideStream* side = (d->I_shared > 0 && use_tc && d->T <= kSharedOverlapMaxTokens && stages == B200MOE_STAGE_ALL)
                          ? side_stream() : nullptr;
   if (side) {
     if (cudaEventRecord(side->fork, st) != cudaSuccess || cudaStreamWaitEvent(side->s, side->fork, 0) != cudaSuccess)
@@ -253,12 +265,16 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
       MoeGemmArgs t = g2;
       if (cvt) t.s0 = sc32 + 2 * nsc, t.scale_dtype = B200MOE_F32;
       t.ksplit = choose_ksplit(L.P, d->E, d->H, d->I);
-      if (t.ksplit > 1) {
+      if (fused) {
+        t.comb32 = acc32;
+        t.comb_w = topk_w;
+        t.comb_wdt = d->w_dtype;
+      } else if (t.ksplit > 1) {
         t.out32 = reinterpret_cast<float*>(ws + L.y32);
         cudaMemsetAsync(t.out32, 0, (size_t)L.P * d->H * sizeof(float), st);
       }
       rc = moe_gemm2_tc(t, st);
-      if (!rc && t.ksplit > 1) rc = moe_f32_rows_to_bf16(g2.out, t.out32, L.P * d->H, st);
+      if (!rc && !fused && t.ksplit > 1) rc = moe_f32_rows_to_bf16(g2.out, t.out32, L.P * d->H, st);
     } else {
       rc = moe_gemm2_simple(g2, d->act_mode, st);
     }
@@ -333,12 +349,16 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
         MoeGemmArgs t = s2;
         if (cvt) t.s0 = ssc32 + 2 * nscs, t.scale_dtype = B200MOE_F32;
         t.ksplit = choose_ksplit(d->T, 1, d->H, d->I_shared);
-        if (t.ksplit > 1) {
+        if (fused) {  // weight 1, identity rows; joins the routed experts' sums in the same fp32 buffer
+          t.comb32 = acc32;
+          t.comb_w = nullptr;
+          t.div = 1;
+        } else if (t.ksplit > 1) {
           t.out32 = reinterpret_cast<float*>(ws + L.s_y32);
           cudaMemsetAsync(t.out32, 0, (size_t)d->T * d->H * sizeof(float), ss);
         }
         rc = moe_gemm2_tc(t, ss);
-        if (!rc && t.ksplit > 1) rc = moe_f32_rows_to_bf16(s2.out, t.out32, d->T * d->H, ss);
+        if (!rc && !fused && t.ksplit > 1) rc = moe_f32_rows_to_bf16(s2.out, t.out32, d->T * d->H, ss);
       } else {
         rc = moe_gemm2_simple(s2, d->act_mode, ss);
       }
@@ -350,8 +370,11 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     }
     add = ws + L.s_y;
   }
-  if (combined && do_comb) {
-    rc = b200moe_combine(out, ws + L.y, topk_w, d->w_dtype, add, d->T, d->k, d->H, stream);
+  if (fused && do_comb) {
+    rc = moe_f32_rows_to_bf16(reinterpret_cast<__nv_bfloat16*>(out), acc32, d->T * d->H, st);
+    if (rc) return rc;
+  } else if (combined && do_comb) {
+    rc = b200moe_combine_masked(out, ws + L.y, nullptr, topk_w, d->w_dtype, add, ids, d->E, d->T, d->k, d->H, stream);
     if (rc) return rc;
   }
   return B200MOE_OK;

@@ -232,8 +232,8 @@ __global__ void identity_offsets_kernel(int32_t* offsets, int T) {
 // out[t,:] = bf16( sum_j w[t,j]*y[t,j,:] (+ add[t,:]) ); one thread per 8 columns (16-byte accesses)
 __global__ void __launch_bounds__(256)
 combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ y, const void* __restrict__ w,
-               int w_dtype, const __nv_bfloat16* __restrict__ add, const int32_t* __restrict__ pos, int64_t T, int k,
-               int H) {
+               int w_dtype, const __nv_bfloat16* __restrict__ add, const int32_t* __restrict__ pos,
+               const int32_t* __restrict__ ids, int E, int64_t T, int k, int H) {
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int hv = H / 8;
   if (idx >= T * hv) return;
@@ -245,6 +245,8 @@ combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict_
   for (int j = 0; j < k; ++j) {
     const float wj = moe_load_as_f32(w, t * k + j, w_dtype);
     const int64_t yr = pos ? (int64_t)pos[t * k + j] : t * k + j;
+    // a slot whose expert id was out of range has no result row (nothing ever wrote it): it contributes nothing
+    if (yr < 0 || (ids && (ids[t * k + j] < 0 || ids[t * k + j] >= E))) continue;
     uint4 raw = *reinterpret_cast<const uint4*>(y + yr * H + c);
     const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -297,9 +299,10 @@ int moe_gemm2_simple(const MoeGemmArgs& a, int act_mode, cudaStream_t st) {
   return moe_launch_status();
 }
 
-extern "C" int b200moe_combine_indexed(void* out, const void* y, const int32_t* pos, const void* w, int w_dtype,
-                                       const void* add, int64_t T, int64_t k, int64_t H, void* stream) {
-  MOE_CHECK_ARG(out && y && w && T >= 0 && k > 0 && H > 0);
+extern "C" int b200moe_combine_masked(void* out, const void* y, const int32_t* pos, const void* w, int w_dtype,
+                                      const void* add, const int32_t* ids, int64_t E, int64_t T, int64_t k, int64_t H,
+                                      void* stream) {
+  MOE_CHECK_ARG(out && y && w && T >= 0 && k > 0 && H > 0 && (!ids || E > 0));
   MOE_CHECK_ARG(w_dtype == B200MOE_F32 || w_dtype == B200MOE_BF16 || w_dtype == B200MOE_F16);
   MOE_CHECK_SHAPE(H % 8 == 0);
   if (!moe_aligned16(out) || !moe_aligned16(y) || (add && !moe_aligned16(add))) return B200MOE_EALIGN;
@@ -307,8 +310,13 @@ extern "C" int b200moe_combine_indexed(void* out, const void* y, const int32_t* 
   const int64_t n = T * (H / 8);
   combine_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
       reinterpret_cast<__nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(y), w, w_dtype,
-      reinterpret_cast<const __nv_bfloat16*>(add), pos, T, (int)k, (int)H);
+      reinterpret_cast<const __nv_bfloat16*>(add), pos, ids, (int)E, T, (int)k, (int)H);
   return moe_launch_status();
+}
+
+extern "C" int b200moe_combine_indexed(void* out, const void* y, const int32_t* pos, const void* w, int w_dtype,
+                                       const void* add, int64_t T, int64_t k, int64_t H, void* stream) {
+  return b200moe_combine_masked(out, y, pos, w, w_dtype, add, nullptr, 0, T, k, H, stream);
 }
 
 extern "C" int b200moe_combine(void* out, const void* y, const void* w, int w_dtype, const void* add, int64_t T,

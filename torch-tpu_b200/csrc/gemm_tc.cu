@@ -63,37 +63,12 @@ struct TcShared {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  float amax[TC_CG][128];
-  alignas(16) uint8_t ostage[128 * 256];  // down GEMM with peer output: one 128 x 128 bf16 half tile on its way to row-wise stores
+  // down GEMM with peer output: one 128 x 128 bf16 half tile on its way to row-wise stores;
+  // gate/up GEMM: the row maxima the epilogue's column groups exchange, float [2][TC_CG][128]
+  alignas(16) uint8_t ostage[128 * 256];
 };
 constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
 static_assert(TC_SMEM_BYTES <= 232448, "more than the 227 KB of shared memory a CTA can have");
-
-// Optional per-role cycle accounting (compile with -DMOE_TC_PROFILE): slot[blockIdx.x*8 + i]
-//   0 producer wait(empty)  1 mma wait(full)  2 mma wait(tmem_empty)  3 mma total
-//   4 epilogue wait(tmem_full)  5 epilogue wake->buffer released  6 epilogue rest (FMAs after release, tile end)
-//   7 epilogue total  8 first two TMEM chunks  9 FMAs + six more chunks  10 loop top  11 fence + release
-#ifdef MOE_TC_PROFILE
-__device__ long long g_tc_prof[256 * 12];
-#define PROF_DECL(v) long long v = 0
-#define PROF_T0(t) long long t = clock64()
-#define PROF_ADD(v, t) v += clock64() - t
-#define PROF_STORE(i, v) if (blockIdx.x < 256) g_tc_prof[blockIdx.x * 12 + (i)] = (v)
-#else
-#define PROF_DECL(v)
-#define PROF_T0(t)
-#define PROF_ADD(v, t)
-#define PROF_STORE(i, v)
-#endif
-// Ablation switches for timing experiments (compile with -DMOE_TC_ABLATE, select with env MOE_TC_DBG):
-// bit 1 constant scales, bit 2 skip tile end, bit 4 skip the B-operand
-// copies, bit 5 skip the MMAs, bit 6 skip all operand copies
-#if defined(MOE_TC_PROFILE) || defined(MOE_TC_ABLATE)
-#define MOE_TC_DBG_ON 1
-#define DBG(bit) ((a.dbg >> (bit)) & 1)
-#else
-#define DBG(bit) false
-#endif
 
 struct TcArgs {
   const float* as_t;
@@ -110,11 +85,15 @@ struct TcArgs {
   int KS;        // K splits (down GEMM of decode-size batches); 1 = none
   int m_major;   // work-item order: 0 = n-tile slow, m-tile fast; 1 = m-tile slow, n-tile fast (see launch_tc)
   float* out32;  // fp32 accumulation target when KS > 1
+  // down GEMM with the weighted combine fused in: row r adds comb_w[pair] * y[r,:] into comb32[pair / div, :] (fp32,
+  // red.global.add; pair = row_map[r] or r, comb_w NULL = weight 1); overrides out / out32
+  float* comb32;
+  const void* comb_w;
+  int comb_wdt, div;
   uint8_t* hq;
   float* hs_t;
   __nv_bfloat16* out;
   int32_t* status;
-  int dbg;  // MOE_TC_PROFILE / MOE_TC_ABLATE builds only: bit 0 skip FMAs, bit 1 constant scales, bit 2 skip tile end
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------
@@ -129,6 +108,12 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+#ifndef MOE_TC_ABL
+#define MOE_TC_ABL 0
+#endif
+#ifndef MOE_TC_PIPE
+#define MOE_TC_PIPE 2
+#endif
 #ifndef MOE_TC_HINT
 #define MOE_TC_HINT 2000
 #endif
@@ -153,6 +138,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
       : "r"(bar), "r"(parity)
       : "memory");
 #endif
+  return ok;
+}
+// non-blocking test of a phase
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
   return ok;
 }
 // Bounded wait.  Returns false when it gave up or another role already did.
@@ -211,7 +208,23 @@ __device__ __forceinline__ void tc_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16])
                :
                : "memory");
 }
-// packed fp32 pairs: one fma.rn.f32x2 does two multiply-adds with one instruction slot
+// A pair of fp32 accumulators.  Two forms: one fma.rn.f32x2 per pair (half the instruction slots) or two scalar
+// FMAs (MOE_TC_SCALAR_FMA; the form the TMEM-read microbenchmark found a little faster on this part).
+#ifndef MOE_TC_SCALAR_FMA
+#define MOE_TC_SCALAR_FMA 1
+#endif
+#if MOE_TC_SCALAR_FMA
+struct acc2_t {
+  float x, y;
+};
+__device__ __forceinline__ acc2_t acc2_zero() { return acc2_t{0.f, 0.f}; }
+__device__ __forceinline__ acc2_t pack2(float lo, float hi) { return acc2_t{lo, hi}; }
+__device__ __forceinline__ acc2_t pack2u(uint32_t lo, uint32_t hi) { return acc2_t{__uint_as_float(lo), __uint_as_float(hi)}; }
+__device__ __forceinline__ float2 unpack2(acc2_t v) { return make_float2(v.x, v.y); }
+__device__ __forceinline__ acc2_t ffma2(acc2_t a, acc2_t b, acc2_t c) { return acc2_t{fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)}; }
+#else
+typedef uint64_t acc2_t;
+__device__ __forceinline__ acc2_t acc2_zero() { return 0ull; }
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
   asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
@@ -232,9 +245,16 @@ __device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
   return d;
 }
-// SiLU with the fast exponential and reciprocal (ex2.approx / rcp.approx): relative error ~1e-6, far inside the
-// rounding of the e4m3 requantisation that follows
-__device__ __forceinline__ float moe_silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+#endif
+// SiLU through one special-function operation per value: x * sigmoid(x) with sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5
+// (tanh.approx.f32, absolute error of the sigmoid below 2^-11: far inside the e4m3 requantisation that follows; the
+// exp + reciprocal form costs two such operations, and the tile end of the gate/up GEMM is bound by that unit)
+__device__ __forceinline__ float moe_silu_fast(float x) {
+  const float hx = 0.5f * x;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(hx));
+  return fmaf(hx, t, hx);
+}
 
 // Shared-memory matrix descriptor of a 128-byte-swizzled operand tile (8-row x 128-byte atoms, 1024 B each).
 //   K-major : rows are M/N indices, 128 B of K per row; SBO = 1024 (next 8 rows); LBO unused (1)
@@ -297,7 +317,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      PROF_DECL(p_wait);
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int ks = t % a.KS, tt = t / a.KS;
         const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
@@ -306,21 +325,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % TC_STAGES;
           const uint32_t ph = (it / TC_STAGES) & 1;
-          PROF_T0(tw);
           if (!mbar_wait(smem_u32(&sh->empty[s]), ph ^ 1, abort_flag)) {
             ok = false;
             break;
           }
-          PROF_ADD(p_wait, tw);
           const uint32_t full = smem_u32(&sh->full[s]);
           const uint32_t sa = smem_base + s * TC_STAGE_BYTES, sb = sa + TC_A_BYTES;
-          if (DBG(6)) {  // no copies at all: the MMAs run on whatever the stage holds
-            mbar_arrive(full);
-            continue;
-          }
-          mbar_arrive_expect_tx(full, DBG(4) ? TC_A_BYTES : TC_STAGE_BYTES);
+          mbar_arrive_expect_tx(full, TC_STAGE_BYTES);
           tma_load_2d(sa, &tmA, kb * kBlock, row0, full);
-          if (DBG(4)) continue;
           if (DENSE) {
             tma_load_2d(sb, &tmB0, kb * kBlock, e * a.I + nt * 256, full);
             tma_load_2d(sb + 128 * 128, &tmB0, kb * kBlock, e * a.I + nt * 256 + 128, full);
@@ -333,7 +345,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
         }
       }
-      PROF_STORE(0, p_wait);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (one thread)
@@ -349,17 +360,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         const int ks = t % a.KS;
         n_it += (uint32_t)((int)((int64_t)KB_all * (ks + 1) / a.KS) - (int)((int64_t)KB_all * ks / a.KS));
       }
-      PROF_DECL(m_wfull);
-      PROF_DECL(m_wtmem);
-      PROF_T0(m_t0);
       for (uint32_t it = 0; it < n_it; ++it) {
         const uint32_t s = it % TC_STAGES, buf = it & 1;
-        PROF_T0(tw1);
         if (!mbar_wait(smem_u32(&sh->full[s]), (it / TC_STAGES) & 1, abort_flag)) break;
-        PROF_ADD(m_wfull, tw1);
-        PROF_T0(tw2);
         if (!mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((it >> 1) & 1) ^ 1, abort_flag)) break;
-        PROF_ADD(m_wtmem, tw2);
         tc_fence_after();
         // the stage's byte offset, in the descriptors' 16-byte units, stays inside the 14-bit address field
         const uint64_t adesc = adesc0 + (uint64_t)(s * (TC_STAGE_BYTES >> 4));
@@ -370,15 +374,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           // K advances 32 elements: +32 B inside the swizzle atom (K-major) or +32 rows of 128 B (MN-major)
           const uint64_t ad = adesc + (uint64_t)(ks * 2);
           const uint64_t bd = bdesc + (uint64_t)(GEMM2 ? ks * 256 : ks * 2);
-          if (!DBG(5)) tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
+          tc_mma_f8(d, ad, bd, idesc, ks > 0 ? 1u : 0u);
         }
         tc_commit(smem_u32(&sh->empty[s]));  // wakes the producer (refill) and the epilogue (accumulator ready)
       }
-      PROF_DECL(m_total);
-      PROF_ADD(m_total, m_t0);
-      PROF_STORE(1, m_wfull);
-      PROF_STORE(2, m_wtmem);
-      PROF_STORE(3, m_total);
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue (4 * TC_CG warps)
@@ -387,15 +386,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const int rit = q * 32 + lane;  // row inside the tile == TMEM lane
     uint32_t it = 0;
     bool ok = true;
-    PROF_DECL(e_wait);
-    PROF_DECL(e_ld);
-    PROF_DECL(e_end);
-    PROF_DECL(e_s1);
-    PROF_DECL(e_s2);
-    PROF_DECL(e_s3);
-    PROF_DECL(e_s4);
-    PROF_T0(e_t0);
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    int ntile = 0;  // work items this CTA has finished
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++ntile) {
       const int ks = t % a.KS, tt = t / a.KS;
       const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
@@ -406,11 +398,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const bool valid = grow < row_end;
       const bool warp_has_rows = row0 + q * 32 < row_end;  // uniform over the warp
       // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's TC_CW-column span of half j
-      uint64_t acc[2][TC_CW / 2];
+      acc2_t acc[2][TC_CW / 2];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = 0ull;
+        for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = acc2_zero();
       // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here.
       // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
       // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
@@ -424,80 +416,148 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                           (int64_t)kb0 * sstep;
       const int64_t w1i = w0i + (GEMM2 ? ((2 * nt + 1 < nH) ? 1 : 0) : DENSE ? ((2 * nt + 1 < nIs) ? nH : 0) : 0);
       auto load_sa = [&](int kb) { return valid ? a.as_t[(int64_t)(kb0 + kb) * a.ld + grow] : 0.f; };
-      // scales are fetched two K blocks ahead (the activation-scale lines come from L2)
-      float sa0 = load_sa(0), sa1 = KB > 1 ? load_sa(1) : 0.f;
-      float wa0 = S0[w0i], wa1 = KB > 1 ? S0[w0i + sstep] : 0.f;
-      float wb0 = S1[w1i], wb1 = KB > 1 ? S1[w1i + sstep] : 0.f;
-      for (int kb = 0; kb < KB; ++kb, ++it) {
-        PROF_T0(ttop);
-        const float f0 = DBG(1) ? 1.f : sa0 * wa0, f1 = DBG(1) ? 1.f : sa0 * wb0;
-        sa0 = sa1, wa0 = wa1, wb0 = wb1;
-        if (kb + 2 < KB && !DBG(1)) {
-          sa1 = load_sa(kb + 2);
-          wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
-          wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
-        }
-        const int buf = it & 1;
-        PROF_ADD(e_s3, ttop);
-        PROF_T0(tw);
-        if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
-          ok = false;
-          break;
-        }
-        PROF_ADD(e_wait, tw);
-        PROF_T0(tl);
-        tc_fence_after();
-        if (!warp_has_rows) {  // decode-size batches: most row quarters are empty; just hand the buffer back
+      // Scale factors f0 = sa[row,kb] * sw_gate[kb], f1 = sa[row,kb] * sw_up[kb]: the products of block kb + 1 are
+      // formed and the values of block kb + 2 are requested while block kb's TMEM loads are in flight.
+      float f0, f1, sa1 = 0.f, wa1 = 0.f, wb1 = 0.f;
+      {
+        const float sa0 = load_sa(0);
+        f0 = sa0 * S0[w0i], f1 = sa0 * S1[w1i];
+        if (KB > 1) sa1 = load_sa(1), wa1 = S0[w0i + sstep], wb1 = S1[w1i + sstep];
+      }
+      if (!warp_has_rows) {
+        // decode-size batches: most row quarters hold no rows; such a warp only hands every buffer straight back
+        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+          if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
-          continue;
+          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[it & 1]));
         }
-        const uint32_t tbase = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256 + cg * TC_CW;
-        const uint64_t f0p = pack2(f0, f0), f1p = pack2(f1, f1);
-        // The thread's 2 x TC_CW columns leave TMEM in 16-column chunks through two 16-register staging sets:
-        // while one set feeds 8 packed FMAs the other set's load is in flight.  (Two 32-register sets overlap a
-        // little more but push the loop over the register file: spills here are L2 round trips.)
+      } else if (ok) {
+        // The thread's 2 x TC_CW columns leave TMEM in 16-column chunks through two 16-register staging sets: while
+        // one set feeds 8 packed FMAs the other set's load is in flight.  The chain runs ACROSS K blocks: the wait for
+        // block kb + 1's accumulator, the scale products and the hand-back of block kb's buffer all sit under loads in
+        // flight, and block kb + 1's first two loads are issued between block kb's last FMAs.  (A warp that walks
+        // wait -> loads -> FMAs -> hand-back strictly block by block spends most of a K block waiting on one of them.)
         uint32_t s0[TC_CH], s1[TC_CH];
-        auto chunk_addr = [&](int c) { return tbase + (c / TC_CPH) * 128 + (c % TC_CPH) * TC_CH; };
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + cg * TC_CW;
+        auto chunk_addr = [&](uint32_t tb, int c) { return tb + (c / TC_CPH) * 128 + (c % TC_CPH) * TC_CH; };
+        acc2_t f0p = acc2_zero(), f1p = acc2_zero();
         auto fma_chunk = [&](int c, const uint32_t (&sv)[TC_CH]) {
-          const uint64_t fp = (c / TC_CPH) ? f1p : f0p;
+          const acc2_t fp = (c / TC_CPH) ? f1p : f0p;
 #pragma unroll
           for (int i = 0; i < TC_CH / 2; ++i)
             acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i] =
                 ffma2(pack2u(sv[2 * i], sv[2 * i + 1]), fp, acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i]);
         };
-        tc_ld_issue(chunk_addr(0), s0);
-        tc_ld_issue(chunk_addr(1), s1);
-        tc_ld_wait(s0, s1);
-        PROF_ADD(e_s1, tl);
-        PROF_T0(t2);
-#pragma unroll
-        for (int c = 0; c < TC_NC - 2; c += 2) {
-          fma_chunk(c, s0);
-          tc_ld_issue(chunk_addr(c + 2), s0);
-          fma_chunk(c + 1, s1);
-          tc_ld_issue(chunk_addr(c + 3), s1);
+#if MOE_TC_PIPE == 0
+        for (int kb = 0; kb < KB && ok; ++kb, ++it) {   // strict order, block by block
+          f0p = pack2(f0, f0), f1p = pack2(f1, f1);
+          const float nf0 = sa1 * wa1, nf1 = sa1 * wb1;
+          if (kb + 2 < KB) {
+            sa1 = load_sa(kb + 2);
+            wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
+            wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
+          }
+          if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tb = lane_base + (it & 1) * 256;
+          tc_ld_issue(chunk_addr(tb, 0), s0);
+          tc_ld_issue(chunk_addr(tb, 1), s1);
           tc_ld_wait(s0, s1);
+#pragma unroll
+          for (int c = 0; c < TC_NC - 2; c += 2) {
+            fma_chunk(c, s0);
+            tc_ld_issue(chunk_addr(tb, c + 2), s0);
+            fma_chunk(c + 1, s1);
+            tc_ld_issue(chunk_addr(tb, c + 3), s1);
+            tc_ld_wait(s0, s1);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[it & 1]));
+          fma_chunk(TC_NC - 2, s0);
+          fma_chunk(TC_NC - 1, s1);
+          f0 = nf0, f1 = nf1;
         }
-        PROF_ADD(e_s2, t2);
-        PROF_T0(t4);
-        tc_fence_before();                   // all of this block is in registers: hand the buffer back
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
-        PROF_ADD(e_s4, t4);
-        PROF_ADD(e_ld, tl);
-        PROF_T0(tp);
-        fma_chunk(TC_NC - 2, s0);
-        fma_chunk(TC_NC - 1, s1);
-        PROF_ADD(e_end, tp);
+#else
+        if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) ok = false;
+        if (ok) {
+          tc_fence_after();
+          const uint32_t tb = lane_base + (it & 1) * 256;
+          tc_ld_issue(chunk_addr(tb, 0), s0);
+          tc_ld_issue(chunk_addr(tb, 1), s1);
+        }
+        for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+          const bool more = kb + 1 < KB;
+          const uint32_t tb = lane_base + (it & 1) * 256;
+          f0p = pack2(f0, f0), f1p = pack2(f1, f1);
+          const float nf0 = sa1 * wa1, nf1 = sa1 * wb1;  // block kb + 1
+          if (kb + 2 < KB && !(MOE_TC_ABL & 1)) {
+            sa1 = load_sa(kb + 2);
+            wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
+            wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
+          }
+          tc_ld_wait(s0, s1);
+#pragma unroll
+          for (int c = 0; c < TC_NC - 2; c += 2) {
+            fma_chunk(c, s0);
+            tc_ld_issue(chunk_addr(tb, c + 2), s0);
+            fma_chunk(c + 1, s1);
+            tc_ld_issue(chunk_addr(tb, c + 3), s1);
+            if (c + 4 < TC_NC) tc_ld_wait(s0, s1);
+          }
+          const uint32_t nbar = smem_u32(&sh->empty[(it + 1) % TC_STAGES]), npar = ((it + 1) / TC_STAGES) & 1;
+#if MOE_TC_PIPE == 1
+          // the last two chunks of this block are in flight: wait for the next block's accumulator meanwhile
+          bool next_ready = more ? mbar_wait(nbar, npar, abort_flag) : false;
+          if (more && !next_ready) ok = false;
+#else
+          // The last two chunks of this block are in flight.  Is the next block's accumulator there already (it is
+          // whenever this warp is what the MMAs wait for)?  Only a test: the buffer goes back before any real wait,
+          // or the MMA issuer, which needs this buffer for block kb + 2, would idle until block kb + 1 is done.
+          const bool next_ready = more && mbar_test(nbar, npar);
+#endif
+          tc_ld_wait(s0, s1);
+          tc_fence_before();  // all of this block is in registers: hand the buffer back
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[it & 1]));
+          if (!ok) break;
+          const uint32_t tn = lane_base + ((it + 1) & 1) * 256;
+          if (next_ready) {
+            tc_fence_after();
+            fma_chunk(TC_NC - 2, s0);
+            tc_ld_issue(chunk_addr(tn, 0), s0);
+            fma_chunk(TC_NC - 1, s1);
+            tc_ld_issue(chunk_addr(tn, 1), s1);
+          } else {
+            fma_chunk(TC_NC - 2, s0);
+            fma_chunk(TC_NC - 1, s1);
+            if (more) {
+              if (!mbar_wait(nbar, npar, abort_flag)) {
+                ok = false;
+                ++it;
+                break;
+              }
+              tc_fence_after();
+              tc_ld_issue(chunk_addr(tn, 0), s0);
+              tc_ld_issue(chunk_addr(tn, 1), s1);
+            }
+          }
+          f0 = nf0, f1 = nf1;
+        }
+#endif
       }
-      if (!ok) break;
-      PROF_T0(te);
-      if (DBG(2)) continue;
+      float amax = 0.f;
       if (MODE == 0) {
-        // SiLU(gate) * up, then 1x128 requantisation: the row's 128 values are split over TC_CG warps
-        float amax = 0.f;
+        // SiLU(gate) * up; the row's 128 values are split over TC_CG warps, which exchange their maxima through
+        // shared memory (two copies, alternating by tile, so that one barrier per tile is enough)
 #pragma unroll
         for (int i = 0; i < TC_CW / 2; ++i) {  // h overwrites the gate accumulators: no second array of 64 registers
           const float2 g = unpack2(acc[0][i]), u = unpack2(acc[1][i]);
@@ -505,12 +565,29 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           acc[0][i] = pack2(hx, hy);
           amax = fmaxf(amax, fmaxf(fabsf(hx), fabsf(hy)));
         }
-        sh->amax[cg][rit] = amax;
-        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
+        reinterpret_cast<float*>(sh->ostage)[((ntile & 1) * TC_CG + cg) * 128 + rit] = amax;
+      }
+      // One decision for all epilogue warps before anything that couples them (the named barriers of the tile end): a
+      // warp whose wait ran out comes here like the others, and if any did, all of them leave together.
+      {
+        uint32_t any_bad;
+        asm volatile(
+            "{\n\t.reg .pred p, r;\n\t"
+            "setp.ne.b32 p, %1, 0;\n\t"
+            "bar.red.or.pred r, 1, %2, p;\n\t"
+            "selp.u32 %0, 1, 0, r;\n\t}"
+            : "=r"(any_bad)
+            : "r"((uint32_t)(ok ? 0 : 1)), "n"(TC_EPI_THREADS)
+            : "memory");
+        if (any_bad) {
+          ok = false;
+          break;
+        }
+      }
+      if (MODE == 0) {
 #pragma unroll
-        for (int o = 0; o < TC_CG; ++o) amax = fmaxf(amax, sh->amax[o][rit]);
+        for (int o = 0; o < TC_CG; ++o) amax = fmaxf(amax, reinterpret_cast<const float*>(sh->ostage)[((ntile & 1) * TC_CG + o) * 128 + rit]);
         amax = fmaxf(amax, kAmaxFloor);
-        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
         const float inv = kFp8Max / amax;
         if (valid) {
           uint4* dst = reinterpret_cast<uint4*>(a.hq + (int64_t)grow * a.I + nt * 128 + cg * TC_CW);
@@ -571,6 +648,25 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
         }
+      } else if (valid && a.comb32) {
+        // Fused weighted combine: the k rows of one token come from different experts, i.e. from different CTAs, so they
+        // meet in an fp32 buffer through 16-byte reductions (their order, and with it the last bit of the sum, is not
+        // fixed).  K-split partial sums take the same way: the combine is linear.
+        const int pair = a.row_map ? a.row_map[grow] : grow;
+        const float w = a.comb_w ? moe_load_as_f32(a.comb_w, pair, a.comb_wdt) : 1.f;
+        float* drow = a.comb32 + (int64_t)(pair / a.div) * a.H;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int col = nt * 256 + j * 128 + cg * TC_CW;
+          if (col >= a.H) continue;
+#pragma unroll
+          for (int v4 = 0; v4 < TC_CW / 4; ++v4) {
+            const float2 p0 = unpack2(acc[j][v4 * 2]), p1 = unpack2(acc[j][v4 * 2 + 1]);
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(drow + col + v4 * 4), "f"(p0.x * w),
+                         "f"(p0.y * w), "f"(p1.x * w), "f"(p1.y * w)
+                         : "memory");
+          }
+        }
       } else if (valid) {
         const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
         __nv_bfloat16* obase = a.out;
@@ -581,10 +677,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (col < OUTW && a.KS > 1) {  // K split: partial sums meet in the fp32 buffer
             float* dst32 = a.out32 + dstrow * OUTW + col;
 #pragma unroll
-            for (int w = 0; w < TC_CW / 2; ++w) {
-              const float2 v = unpack2(acc[j][w]);
-              atomicAdd(dst32 + 2 * w, v.x);
-              atomicAdd(dst32 + 2 * w + 1, v.y);
+            for (int v4 = 0; v4 < TC_CW / 4; ++v4) {
+              const float2 p0 = unpack2(acc[j][v4 * 2]), p1 = unpack2(acc[j][v4 * 2 + 1]);
+              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst32 + v4 * 4), "f"(p0.x), "f"(p0.y),
+                           "f"(p1.x), "f"(p1.y)
+                           : "memory");
             }
           } else if (col < OUTW) {
             uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * OUTW + col);
@@ -602,19 +699,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
         }
       }
-      PROF_ADD(e_end, te);
-    }
-    if (warp == 4 && lane == 0) {
-      PROF_DECL(e_total);
-      PROF_ADD(e_total, e_t0);
-      PROF_STORE(4, e_wait);
-      PROF_STORE(5, e_ld);
-      PROF_STORE(6, e_end);
-      PROF_STORE(7, e_total);
-      PROF_STORE(8, e_s1);
-      PROF_STORE(9, e_s2);
-      PROF_STORE(10, e_s3);
-      PROF_STORE(11, e_s4);
     }
   }
 
@@ -663,14 +747,31 @@ bool make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols)
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int device_sm_count() {
-  static int n = [] {
-    int dev = 0, v = 0;
-    cudaGetDevice(&dev);
+// Per-device facts and one-time set-up, indexed by the CUDA device ordinal: a process that drives several GPUs comes
+// here with each of them current in turn (the dynamic shared-memory cap of a kernel is a per-device attribute).
+constexpr int kMaxDevices = 64;
+struct DeviceInfo {
+  int sm_count = 0;  // 0 = not looked up yet
+  bool tc_ok = false, attr_set = false;
+};
+DeviceInfo* device_info() {
+  static DeviceInfo tab[kMaxDevices];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  DeviceInfo& d = tab[dev];
+  if (d.sm_count == 0) {
+    int v = 0, major = 0;
     cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
-    return v > 0 ? v : 1;
-  }();
-  return n;
+    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    d.tc_ok = major == 10 && get_encode_fn() != nullptr;
+    d.sm_count = v > 0 ? v : 1;
+  }
+  return &d;
+}
+
+int device_sm_count() {
+  DeviceInfo* d = device_info();
+  return d ? d->sm_count : 1;
 }
 
 template <int MODE>
@@ -696,7 +797,11 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.H = g.H;
   a.I = g.I;
   a.NT = GEMM2 ? (g.H + 255) / 256 : DENSE ? (g.I + 255) / 256 : g.I / 128;
-  a.KS = (GEMM2 && g.ksplit > 1 && g.out32 && !g.row_src) ? g.ksplit : 1;
+  a.comb32 = (GEMM2 && !g.row_src) ? g.comb32 : nullptr;
+  a.comb_w = g.comb_w;
+  a.comb_wdt = g.comb_wdt;
+  a.div = g.div > 0 ? g.div : 1;
+  a.KS = (GEMM2 && g.ksplit > 1 && (g.out32 || a.comb32) && !g.row_src) ? g.ksplit : 1;
   // Work-item order.  The CTAs that run together hold about one SM count of consecutive work items.  With the
   // n-tile as the slow index they share a few weight tiles and sweep ALL rows of A once per group of n-tiles: right
   // while A stays in L2.  When A is larger than that (prefill-size down GEMM: P x I bytes; many-token gate/up GEMM
@@ -714,15 +819,13 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.hs_t = g.hs_t;
   a.out = g.out;
   a.status = g.status;
-#ifdef MOE_TC_DBG_ON
-  a.dbg = getenv("MOE_TC_DBG") ? atoi(getenv("MOE_TC_DBG")) : 0;
-#endif
-  static bool attr = false;
-  if (!attr) {
+  DeviceInfo* di = device_info();
+  if (!di) return B200MOE_EDRIVER;
+  if (!di->attr_set) {
     cudaFuncSetAttribute(moe_gemm_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
     cudaFuncSetAttribute(moe_gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
     cudaFuncSetAttribute(moe_gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TC_SMEM_BYTES);
-    attr = true;
+    di->attr_set = true;
   }
   const long long max_tiles = (long long)g.max_mtiles * a.NT * a.KS;
   const int grid = (int)(max_tiles < device_sm_count() ? max_tiles : device_sm_count());
@@ -732,20 +835,9 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
 
 }  // namespace
 
-#ifdef MOE_TC_PROFILE
-extern "C" int b200moe_debug_read_tc_profile(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, g_tc_prof, sizeof(long long) * 256 * 12);
-}
-#endif
-
 bool moe_tc_available() {
-  static bool ok = [] {
-    int dev = 0, major = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return false;
-    cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    return major == 10 && get_encode_fn() != nullptr;
-  }();
-  return ok;
+  DeviceInfo* d = device_info();
+  return d && d->tc_ok;
 }
 
 namespace {

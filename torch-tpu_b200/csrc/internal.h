@@ -33,6 +33,11 @@ struct MoeGemmArgs {
   __nv_bfloat16* out;       // gemm2: bf16 rows of H, row index = row_map ? row_map[r] : r
   int ksplit;               // gemm2 (tensor-core path): > 1 splits K over CTAs, partial sums added into out32
   float* out32;             // fp32 [rows,H], zero on entry, same row indexing as out (needed when ksplit > 1)
+  // gemm2 with the weighted combine fused in (tensor-core path only): row r adds comb_w[pair] * y[r,:] into
+  // comb32[pair / div, :], pair = row_map ? row_map[r] : r; comb32 fp32 [T,H], zero on entry; comb_w NULL = weight 1
+  float* comb32;
+  const void* comb_w;
+  int comb_wdt;
   // gemm2 over peer memory (tensor-core path only): row r goes to rank (row_src[r] >> 24), row (row_src[r] & 0xFFFFFF)
   // of that rank's buffer out_tbl[rank] (bf16 rows of H); overrides out/row_map
   const int32_t* row_src;

@@ -13,7 +13,9 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <algorithm>
 #include <unordered_map>
+#include <utility>
 
 #include "../../include/b200moe.h"
 
@@ -65,6 +67,44 @@ Tensor workspace_for(const Device& dev, cudaStream_t st, size_t bytes) {
   return it->second;
 }
 
+// One int32 status word per device (see the status bits in b200moe.h), handed to every experts call.  Expert ids
+// outside [0,E) never index anything (the permutation drops them) and raise bit 0 here.  The op stays asynchronous
+// by default; with MOE_CHECK_STATUS=1 it synchronises after every call and raises, which is what a debugging session
+// wants.  my_ops.b200_moe_status() returns the word's tensor.
+Tensor status_word(const Device& dev) {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> words;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(dev.index());
+  if (it == words.end()) it = words.emplace(dev.index(), at::zeros({1}, TensorOptions().dtype(kInt).device(dev))).first;
+  return it->second;
+}
+
+bool check_status_from_env() {
+  const char* v = std::getenv("MOE_CHECK_STATUS");
+  return v && v[0] == '1';
+}
+
+// fp32 copies of bf16 block scales, made once per scale tensor (keyed by storage address, size and version counter)
+// instead of on every call: the tensor-core kernels read fp32 scales only.
+Tensor scales_as_f32(const Tensor& s) {
+  if (s.scalar_type() == kFloat) return s;
+  struct Entry {
+    int64_t numel;
+    uint32_t version;
+    Tensor f32;
+  };
+  static std::mutex mu;
+  static std::unordered_map<const void*, Entry> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(s.data_ptr());
+  if (it == cache.end() || it->second.numel != s.numel() || it->second.version != s._version()) {
+    if (cache.size() > 64) cache.clear();
+    it = cache.insert_or_assign(s.data_ptr(), Entry{s.numel(), (uint32_t)s._version(), s.to(kFloat)}).first;
+  }
+  return it->second.f32;
+}
+
 Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, const Tensor& up_w,
                    const Tensor& down_w, const Tensor& gate_s, const Tensor& up_s, const Tensor& down_s,
                    const Tensor& select_experts, const Tensor& routing_weights, int64_t blocksize,
@@ -102,6 +142,10 @@ Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, co
               "select_experts must be [T,k]");
   TORCH_CHECK(routing_weights.numel() == T * top_k, "routing_weights must be [T,k]");
 
+  // the FP8 tensor-core path reads fp32 scales: convert bf16 ones once per tensor, not per call
+  const bool to_f32 = act_mode == B200MOE_ACT_W8A8 && gate_s.scalar_type() == kBFloat16;
+  const Tensor gs = to_f32 ? scales_as_f32(gate_s) : gate_s, us = to_f32 ? scales_as_f32(up_s) : up_s,
+               ds = to_f32 ? scales_as_f32(down_s) : down_s;
   b200moe_experts_desc d{};
   d.T = T;
   d.H = H;
@@ -118,7 +162,7 @@ Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, co
   }
   d.act_mode = act_mode;
   d.impl = B200MOE_IMPL_AUTO;
-  d.scale_dtype = scale_dtype_of(gate_s);
+  d.scale_dtype = scale_dtype_of(gs);
   if (routing_weights.scalar_type() == kFloat) d.w_dtype = B200MOE_F32;
   else if (routing_weights.scalar_type() == kBFloat16) d.w_dtype = B200MOE_BF16;
   else TORCH_CHECK(false, "routing_weights must be float32 or bfloat16");
@@ -130,11 +174,19 @@ Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, co
   Tensor ws = workspace_for(input.device(), st, need);
   void* wsp = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 255) & ~uintptr_t(255));
   const size_t ws_bytes = (size_t)ws.numel() - (reinterpret_cast<char*>(wsp) - reinterpret_cast<char*>(ws.data_ptr()));
+  Tensor status = status_word(input.device());
   int rc = b200moe_experts(output.data_ptr(), input.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(),
-                           down_w.data_ptr(), gate_s.data_ptr(), up_s.data_ptr(), down_s.data_ptr(),
+                           down_w.data_ptr(), gs.data_ptr(), us.data_ptr(), ds.data_ptr(),
                            select_experts.data_ptr<int32_t>(), routing_weights.data_ptr(), nullptr, nullptr,
-                           nullptr, nullptr, nullptr, nullptr, &d, wsp, ws_bytes, nullptr, st);
+                           nullptr, nullptr, nullptr, nullptr, &d, wsp, ws_bytes, status.data_ptr<int32_t>(), st);
   check_rc(rc, "b200moe_experts");
+  if (check_status_from_env()) {
+    const int sw = status.item<int>();
+    status.zero_();
+    TORCH_CHECK((sw & 1) == 0, "fused_moe_fused_experts: select_experts holds ids outside [0, num_experts); "
+                               "those (token,slot) pairs were skipped");
+    TORCH_CHECK(sw == 0, "fused_moe_fused_experts: device status word ", sw, " (a bounded wait inside a kernel gave up)");
+  }
   return output;
 }
 
@@ -271,8 +323,21 @@ Tensor dense_mlp(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& 
   TORCH_CHECK(input.dim() == 2 && gate_weight.dim() == 2, "input [T,H], weights [I,H]");
   TORCH_CHECK(output.dim() == 2 && output.sizes() == input.sizes(), "output must be [T,H]");
   const int64_t T = input.size(0);
-  Tensor ids = at::zeros({T, 1}, input.options().dtype(kInt));
-  Tensor w = at::ones({T, 1}, input.options().dtype(kFloat));
+  // expert id 0 and weight 1 for every row: grow-only constants per device, so that the op allocates nothing per call
+  static std::mutex mu;
+  static std::unordered_map<int, std::pair<Tensor, Tensor>> consts;
+  Tensor ids, w;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto& c = consts[input.device().index()];
+    if (!c.first.defined() || c.first.size(0) < T) {
+      const int64_t cap = std::max<int64_t>(T, 1024);
+      c.first = at::zeros({cap, 1}, input.options().dtype(kInt));
+      c.second = at::ones({cap, 1}, input.options().dtype(kFloat));
+    }
+    ids = c.first.narrow(0, 0, T);
+    w = c.second.narrow(0, 0, T);
+  }
   Tensor out3 = output.view({T, 1, input.size(1)});
   Tensor gw = gate_weight.unsqueeze(0), uw = up_weight.unsqueeze(0), dw = down_weight.unsqueeze(0);
   Tensor gs = gate_scale.unsqueeze(0), us = up_scale.unsqueeze(0), ds = down_scale.unsqueeze(0);
@@ -327,7 +392,14 @@ Tensor mm_w8a16_dq_forward(Tensor& input, Tensor& weight, Tensor& scale, Tensor&
   return output;
 }
 
+// The device status word of the current device (int32 [1]; bits in include/b200moe.h).  Not part of the reference's
+// surface: the reference reports device errors through its runtime, this library through that word.
+Tensor b200_moe_status() {
+  return status_word(Device(kCUDA, (c10::DeviceIndex)at::cuda::current_device()));
+}
+
 TORCH_LIBRARY(my_ops, m) {
+  m.def("b200_moe_status", b200_moe_status);
   m.def("fused_moe_grouped_topk", fused_moe_grouped_topk);
   m.def("fused_moe_fused_experts", fused_moe_fused_experts);
   m.def("fused_moe_fused_experts_v2", fused_moe_fused_experts_v2);

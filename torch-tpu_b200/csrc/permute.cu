@@ -14,6 +14,7 @@ namespace {
 
 constexpr int kChunk = 1024;  // pairs per CTA (32 warps)
 constexpr int kMaxE = 1024;
+constexpr int kMaxDevices = 64;  // per-device caches below are indexed by the CUDA device ordinal
 
 // Per-warp histogram of this chunk in shared memory: wh[w*E + e].  Returns the pair's expert (or -1)
 // and its rank among equal experts in lower lanes of its warp.
@@ -102,6 +103,9 @@ permute_scatter_kernel(const int32_t* __restrict__ ids, int64_t P, int E,
     int pos = offsets[e] + chunk_base[(int64_t)blockIdx.x * E + e] + wh[(threadIdx.x >> 5) * E + e] + rank;
     sorted_pair[pos] = (int32_t)p;
   }
+  // Pairs whose id was out of range have no position: the tail [offsets[E], P) is filled with -1 so that no consumer
+  // ever indexes with an unwritten entry (valid positions all lie below offsets[E], so this does not race with them).
+  if (p < P && p >= offsets[E]) sorted_pair[p] = -1;
 }
 
 // P <= 1024: histogram, scan and scatter in one CTA
@@ -126,6 +130,7 @@ permute_small_kernel(const int32_t* __restrict__ ids, int64_t P, int E, int32_t*
   __syncthreads();
   for (int i = threadIdx.x; i <= E; i += blockDim.x) offsets[i] = soffs[i];
   if (e >= 0) sorted_pair[soffs[e] + wh[(threadIdx.x >> 5) * E + e] + rank] = (int32_t)threadIdx.x;
+  if ((int64_t)threadIdx.x < P && (int)threadIdx.x >= soffs[E]) sorted_pair[threadIdx.x] = -1;  // dropped pairs: see above
 }
 
 __global__ void gather_scatter_index_kernel(int32_t* __restrict__ gather_index,
@@ -157,6 +162,7 @@ quant_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ s_t, int64_t ld,
   const int64_t r = w / warps_per_row;
   if (r >= rows) return;
   const int c_begin = (int)(w - r * warps_per_row) * cpw * 256;
+  if (row_map && row_map[r] < 0) return;  // position of a dropped pair (id out of range): no row
   const int64_t src = row_map ? (int64_t)(row_map[r] / div) : r;
   const __nv_bfloat16* xr = x + src * H;
   for (int c0 = c_begin; c0 < c_begin + cpw * 256 && c0 < H; c0 += 256) {
@@ -202,12 +208,15 @@ extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, co
   MOE_CHECK_SHAPE(E <= kMaxE && P < (1 << 24));
   cudaStream_t st = (cudaStream_t)stream;
   const size_t smem = (size_t)32 * E * sizeof(int);
-  static bool attr_done = false;  // raising the dynamic shared-memory cap is per-function, idempotent
-  if (!attr_done) {
+  // The dynamic shared-memory cap of a kernel is a per-DEVICE attribute: set it once on every device that comes here.
+  static bool attr_done[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200MOE_EDRIVER;
+  if (!attr_done[dev]) {
     cudaFuncSetAttribute(permute_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
     cudaFuncSetAttribute(permute_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
     cudaFuncSetAttribute(permute_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * kMaxE * 4);
-    attr_done = true;
+    attr_done[dev] = true;
   }
   if (P <= kChunk) {
     permute_small_kernel<<<1, kChunk, smem, st>>>(ids, P, (int)E, expert_offsets, sorted_pair, status);
@@ -249,8 +258,7 @@ extern "C" int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void
 
 // ---- permutation without caller-provided scratch ---------------------------------------------------
 // For hosts that must not (or cannot) allocate device memory around the call - a serving process whose
-// memory pool is fixed at start-up, code running inside a stream capture, a plugin that is only handed
-// input and output buffers.  The chunk-count table that b200moe_permute takes from the caller lives here in
+// memory pool is fixed at start-up, a plugin that is only handed input and output buffers.  The chunk-count table that b200moe_permute takes from the caller lives here in
 // a fixed array inside the library image instead; every GPU that loads the library holds these 256 KB until
 // the process exits.
 constexpr size_t kStaticScratchInts = 64 * 1024;  // 256 KB: e.g. 65536 pairs x 1024 experts, 262144 pairs x 256
@@ -260,7 +268,6 @@ namespace {
 // In host code `g_permute_scratch` is only a handle for the runtime, not a device address, so the address the
 // kernels need is looked up once per device, with that device current.
 int static_scratch_ptr(int32_t** out) {
-  constexpr int kMaxDevices = 64;
   static int32_t* ptrs[kMaxDevices] = {};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);

@@ -108,12 +108,12 @@ class EPFusedMoE:
         send, recv = self.split_sizes(offsets)
         rows = be.pack(x, sorted_pair, ids, self.El)
         RB = rows.shape[1]
-        R = int(sum(recv))
+        R, S = int(sum(recv)), int(sum(send))   # S < T*k when ids outside [0,E) were dropped by the permutation
         recv_rows = torch.empty(max(R, 1), RB, dtype=torch.uint8, device=x.device)
-        dist.all_to_all_single(recv_rows[:R], rows, recv, send, group=self.group)
+        dist.all_to_all_single(recv_rows[:R], rows[:S], recv, send, group=self.group)
         y_recv = be.local_mlp(recv_rows, R, H, layer.w)
         y_back = torch.empty(max(T * ids.shape[1], 1), H, dtype=torch.bfloat16, device=x.device)
-        dist.all_to_all_single(y_back[:T * ids.shape[1]], y_recv.contiguous(), send, recv, group=self.group)
+        dist.all_to_all_single(y_back[:S], y_recv.contiguous(), send, recv, group=self.group)
         add = be.shared_mlp(x, layer.shared) if layer.shared is not None else None
         return be.combine(y_back, sorted_pair, w, add)
 

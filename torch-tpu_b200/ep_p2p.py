@@ -204,7 +204,9 @@ class P2PFusedMoE:
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
                                         p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier2")
-        out = ops.combine(self.y[:T], w, add=add, out=None if self._static is None else self._static["out"][:T])
+        # slots whose expert id was out of range were never dispatched: their rows of y hold nothing and are skipped
+        out = ops.combine_indexed(self.y[:T].view(T * self.k, H), None, w, add=add, ids=ids, num_experts=E,
+                                  out=None if self._static is None else self._static["out"][:T])
         self._mark("combine")
         return out
 

@@ -32,12 +32,13 @@ class FusedMoE:
 
     def __init__(self, cfg: MoEConfig, router_w, wg, wu, wd, sg, su, sd, bias=None, shared: Optional[Tuple] = None,
                  logit_bias=None, max_tokens: int = 4096, act_mode: int = L.ACT_W8A8, impl: int = L.IMPL_AUTO,
-                 alloc_workspace: bool = True):
+                 alloc_workspace: bool = True, fused_combine: bool = False):
         self.cfg = cfg
         self.router_w, self.bias, self.logit_bias = router_w, bias, logit_bias
         self.w = (wg, wu, wd, sg, su, sd)
         self.shared = shared
         self.act_mode, self.impl = act_mode, impl
+        self.fused_combine = fused_combine  # weighted combine inside the down GEMM's epilogue (see ops.experts)
         dev = wg.device
         self.device = dev
         self.max_tokens = max_tokens
@@ -52,7 +53,7 @@ class FusedMoE:
         self.workspace = None
         if alloc_workspace:  # an expert-parallel shard runs its experts through other entry points
             d = ops.make_desc(max_tokens, H, cfg.intermediate, E, k, I_shared=cfg.shared_intermediate,
-                              out_mode=L.OUT_COMBINED, act_mode=act_mode, impl=impl, scale_dtype=sg.dtype)
+                              out_mode=L.OUT_COMBINED_FUSED if fused_combine else L.OUT_COMBINED, act_mode=act_mode, impl=impl, scale_dtype=sg.dtype)
             self.workspace = torch.empty(ops.experts_workspace_bytes(d) + 256, dtype=torch.uint8, device=dev)
 
     def route(self, x):
@@ -72,7 +73,8 @@ class FusedMoE:
             out = self.out[:T]
         wg, wu, wd, sg, su, sd = self.w
         return ops.experts(out, x, wg, wu, wd, sg, su, sd, ids, w, shared=self.shared, act_mode=self.act_mode,
-                           impl=self.impl, workspace=self.workspace, status=self.status)
+                           impl=self.impl, workspace=self.workspace, status=self.status,
+                           fused_combine=self.fused_combine)
 
     __call__ = forward
 

@@ -10,10 +10,12 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
+ABI_VERSION = 2
 OK, EINVAL, ESHAPE, EWORKSPACE, EALIGN, EDRIVER = 0, -1, -2, -3, -4, -5
 F32, BF16, F16 = 0, 1, 2
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
-OUT_PER_SLOT, OUT_COMBINED = 0, 1
+OUT_PER_SLOT, OUT_COMBINED, OUT_COMBINED_FUSED = 0, 1, 2
+STAGE_PREP, STAGE_GATE_UP, STAGE_DOWN, STAGE_COMBINE, STAGE_ALL = 1, 2, 4, 8, 15
 ACT_W8A8, ACT_W8A16 = 0, 1
 IMPL_AUTO, IMPL_SIMPLE, IMPL_TCGEN05 = 0, 1, 2
 STATUS_BAD_EXPERT, STATUS_WAIT_TIMEOUT, STATUS_PEER_TIMEOUT, STATUS_PEER_OVERFLOW = 1, 2, 4, 8
@@ -22,7 +24,8 @@ STATUS_BAD_EXPERT, STATUS_WAIT_TIMEOUT, STATUS_PEER_TIMEOUT, STATUS_PEER_OVERFLO
 class ExpertsDesc(Structure):
     _fields_ = [("T", c_int64), ("H", c_int64), ("I", c_int64), ("E", c_int64), ("k", c_int64),
                 ("I_shared", c_int64), ("out_mode", c_int), ("act_mode", c_int), ("impl", c_int),
-                ("scale_dtype", c_int), ("w_dtype", c_int), ("reserved", c_int)]
+                ("scale_dtype", c_int), ("w_dtype", c_int), ("impl_gate_up", c_int), ("impl_down", c_int),
+                ("stages", c_int)]
 
 
 # name -> (restype, argtypes): every symbol include/b200moe.h declares
@@ -50,6 +53,8 @@ SIGNATURES = {
                                 c_void_p]),
     "b200moe_combine_indexed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64,
                                         c_int64, c_void_p]),
+    "b200moe_combine_masked": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int64, c_void_p]),
     "b200moe_grouped_mlp_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64, c_int64, c_int]),
     "b200moe_grouped_mlp": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p] + [c_void_p] * 6 +
                             [c_int, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p, c_size_t, c_void_p, c_void_p]),
@@ -92,7 +97,7 @@ def lib():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(l, name)
             fn.restype, fn.argtypes = res, args
-        if l.b200moe_abi_version() != 1:
+        if l.b200moe_abi_version() != ABI_VERSION:
             raise RuntimeError("libb200moe.so ABI version mismatch; rebuild it")
         _lib = l
     return _lib

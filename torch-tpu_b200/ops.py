@@ -115,8 +115,10 @@ def quant_rows(x, row_map=None, div=1):
 
 
 def make_desc(T, H, I, E, k, *, I_shared=0, out_mode=L.OUT_PER_SLOT, act_mode=L.ACT_W8A8, impl=L.IMPL_AUTO,
-              scale_dtype=torch.float32, w_dtype=torch.float32, reserved=0):
-    return L.ExpertsDesc(T, H, I, E, k, I_shared, out_mode, act_mode, impl, _DT[scale_dtype], _DT[w_dtype], reserved)
+              scale_dtype=torch.float32, w_dtype=torch.float32, impl_gate_up=L.IMPL_AUTO, impl_down=L.IMPL_AUTO,
+              stages=0):
+    return L.ExpertsDesc(T, H, I, E, k, I_shared, out_mode, act_mode, impl, _DT[scale_dtype], _DT[w_dtype],
+                         impl_gate_up, impl_down, stages)
 
 
 def experts_workspace_bytes(desc):
@@ -124,10 +126,13 @@ def experts_workspace_bytes(desc):
 
 
 def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, act_mode=L.ACT_W8A8,
-            impl=L.IMPL_AUTO, workspace=None, status=None, reserved=0):
+            impl=L.IMPL_AUTO, workspace=None, status=None, fused_combine=False, impl_gate_up=L.IMPL_AUTO,
+            impl_down=L.IMPL_AUTO, stages=0):
     """Everything after routing (reference op my_ops.fused_moe_fused_experts, my_ops/fusedMoE.cpp:117-236).
     ``out`` [T,k,H] -> un-weighted per-slot rows; ``out`` [T,H] -> weighted combine with ``topk_w`` (+ ``shared`` =
-    (wg,wu,wd,sg,su,sd) of a dense expert applied to every token).  Returns ``out``."""
+    (wg,wu,wd,sg,su,sd) of a dense expert applied to every token), formed by a separate kernel in slot order or,
+    with ``fused_combine``, inside the down GEMM's epilogue (fp32 reductions, order not fixed).  ``stages``: a
+    mask of ``L.STAGE_*`` to re-run part of a call on a workspace that a whole call has filled.  Returns ``out``."""
     _chk(out, "out", torch.bfloat16)
     _chk(x, "x", torch.bfloat16)
     for n, t in (("wg", wg), ("wu", wu), ("wd", wd)):
@@ -138,11 +143,11 @@ def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, ac
     T, H = x.shape
     E, I, _ = wg.shape
     k = ids.shape[1]
-    out_mode = L.OUT_PER_SLOT if out.dim() == 3 else L.OUT_COMBINED
+    out_mode = L.OUT_PER_SLOT if out.dim() == 3 else (L.OUT_COMBINED_FUSED if fused_combine else L.OUT_COMBINED)
     I_shared = shared[0].shape[-2] if shared is not None else 0
     d = make_desc(T, H, I, E, k, I_shared=I_shared, out_mode=out_mode, act_mode=act_mode, impl=impl,
                   scale_dtype=sg.dtype, w_dtype=topk_w.dtype if topk_w is not None else torch.float32,
-                  reserved=reserved)
+                  impl_gate_up=impl_gate_up, impl_down=impl_down, stages=stages)
     need = experts_workspace_bytes(d)
     if need == 0 and T > 0:
         raise ValueError("unsupported sizes for b200moe_experts (H, I multiples of 128; see include/b200moe.h)")
@@ -167,15 +172,16 @@ def combine(y, w, add=None, out=None):
     return out
 
 
-def combine_indexed(y, pos, w, add=None, out=None):
-    """out[t,:] = sum_j w[t,j] * y[pos[t*k+j], :] (+ add[t,:]); y bf16 [R,H], pos int32 [T*k] or None."""
+def combine_indexed(y, pos, w, add=None, out=None, ids=None, num_experts=0):
+    """out[t,:] = sum_j w[t,j] * y[pos[t*k+j], :] (+ add[t,:]); y bf16 [R,H], pos int32 [T*k] or None.  Slots with a
+    negative ``pos`` or (when ``ids`` is given) an expert id outside [0, num_experts) contribute nothing."""
     _chk(y, "y", torch.bfloat16)
     T, k = w.shape
     H = y.shape[-1]
     if out is None:
         out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
-    L.check(L.lib().b200moe_combine_indexed(_ptr(out), _ptr(y), _ptr(pos), _ptr(w), _DT[w.dtype], _ptr(add), T, k, H,
-                                            _stream()), "b200moe_combine_indexed")
+    L.check(L.lib().b200moe_combine_masked(_ptr(out), _ptr(y), _ptr(pos), _ptr(w), _DT[w.dtype], _ptr(add), _ptr(ids),
+                                           num_experts, T, k, H, _stream()), "b200moe_combine_masked")
     return out
 
 
