@@ -68,10 +68,10 @@ class CudaBackend:
         self.ops.experts(out, x, *shared, ids)
         return out.view(T, H)
 
-    def combine(self, y_back, sorted_pair, w, add):
+    def combine(self, y_back, sorted_pair, w, add, out=None):
         inv = torch.empty_like(sorted_pair)
         self.ops.invert_permutation(inv, sorted_pair, sorted_pair.numel())
-        return self.ops.combine_indexed(y_back, inv, w, add=add)
+        return self.ops.combine_indexed(y_back, inv, w, add=add, out=out)
 
 
 class EPFusedMoE:
@@ -100,7 +100,7 @@ class EPFusedMoE:
         self.last_counts = allc
         return allc[self.rank].tolist(), allc[:, self.rank].tolist()
 
-    def forward(self, x):
+    def forward(self, x, out=None):
         be, layer = self.backend, self.layer
         T, H = x.shape
         ids, w = be.route(layer, x)                                   # ids over GLOBAL experts
@@ -115,7 +115,7 @@ class EPFusedMoE:
         y_back = torch.empty(max(T * ids.shape[1], 1), H, dtype=torch.bfloat16, device=x.device)
         dist.all_to_all_single(y_back[:S], y_recv.contiguous(), send, recv, group=self.group)
         add = be.shared_mlp(x, layer.shared) if layer.shared is not None else None
-        return be.combine(y_back, sorted_pair, w, add)
+        return be.combine(y_back, sorted_pair, w, add) if out is None else be.combine(y_back, sorted_pair, w, add, out=out)
 
     __call__ = forward
 
@@ -127,31 +127,3 @@ class EPFusedMoE:
     def host_join(self):
         from .layer import _host_pipeline_join
         _host_pipeline_join(self)
-
-
-def build_ep_layer(wl: dict, T: int, dev: str, rank: int, world: int, seed: int = 0, transport: str = "nccl"):
-    """Benchmark helper: the rank's shard of a synthetic layer of workload ``wl`` (see bench.py).  Expert weights are
-    seeded per (seed, first local expert), the replicated router/bias/shared expert by ``seed`` alone.
-    ``transport``: "nccl" (all_to_all_single) or "p2p" (peer-memory stores, ep_p2p.P2PFusedMoE)."""
-    import torch
-    from . import weights as W
-    from .layer import FusedMoE, MoEConfig
-    E = wl["E"]
-    El = E // world
-    w = W.random_experts(El, wl["H"], wl["I"], dev, seed=seed * 1000 + rank * El)
-    g = torch.Generator(device=dev).manual_seed(seed + 12345)
-    wr = (torch.randn(E, wl["H"], generator=g, device=dev) * 0.02).to(torch.bfloat16)
-    bias = torch.randn(E, generator=g, device=dev) * 0.01 if wl["score"] == "sigmoid" else None
-    logit_bias = None
-    if wl.get("zipf"):
-        ranks = (torch.randperm(E, generator=torch.Generator().manual_seed(seed * 31 + 5)) + 1).double()
-        p = ranks ** -1.2
-        logit_bias = (3.0 * torch.log(p / p.sum())).float().to(dev)
-    shared = W.random_experts(1, wl["H"], wl["shared"], dev, seed=seed + 777) if wl.get("shared") else None
-    cfg = MoEConfig(wl["H"], wl["I"], E, wl["k"], wl["score"], wl.get("groups", 1), wl.get("topk_groups", 1), True,
-                    wl.get("scale", 1.0), wl.get("shared", 0))
-    layer = FusedMoE(cfg, wr, *w, bias=bias, shared=shared, logit_bias=logit_bias, max_tokens=T, alloc_workspace=False)
-    if transport == "p2p":
-        from .ep_p2p import P2PFusedMoE
-        return P2PFusedMoE(layer, E, max_tokens=T)
-    return EPFusedMoE(layer, E)

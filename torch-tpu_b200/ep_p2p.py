@@ -150,7 +150,8 @@ class P2PFusedMoE:
             e.record()
             self.phase_events.append((name, e))
 
-    def forward(self, x):
+    def forward(self, x, out=None):
+        """x bf16 [T,H] on the device -> bf16 [T,H] (``out`` if given, else a buffer of this object / a new tensor)."""
         layer, a, lib = self.layer, self.arena, L.lib()
         T, H = x.shape
         if T > self.max_tokens or H != self.H:
@@ -206,7 +207,8 @@ class P2PFusedMoE:
         self._mark("barrier2")
         # slots whose expert id was out of range were never dispatched: their rows of y hold nothing and are skipped
         out = ops.combine_indexed(self.y[:T].view(T * self.k, H), None, w, add=add, ids=ids, num_experts=E,
-                                  out=None if self._static is None else self._static["out"][:T])
+                                  out=out if out is not None else
+                                  (None if self._static is None else self._static["out"][:T]))
         self._mark("combine")
         return out
 

@@ -147,8 +147,7 @@ def _host_pipeline_call(obj, fwd, x_host, out_host):
         st["x_ready"][i].record(st["h2d"])
     cur.wait_event(st["x_ready"][i])
     cur.wait_event(st["y_free"][i])                  # the D2H that read this output buffer two calls ago is done
-    y = fwd(xb)
-    yb.copy_(y)                                      # device-to-device into the pipeline's own output buffer
+    fwd(xb, out=yb)                                  # the layer writes straight into the pipeline's output buffer
     st["x_free"][i].record(cur)
     st["y_ready"][i].record(cur)
     st["d2h"].wait_event(st["y_ready"][i])
