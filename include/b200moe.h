@@ -242,6 +242,16 @@ size_t b200moe_linear_workspace_bytes(int64_t M, int64_t K, int64_t N, int scale
 int b200moe_linear_w8(void* out, const void* x, const void* w, const void* scale, int scale_dtype, int64_t M,
                       int64_t K, int64_t N, void* workspace, size_t workspace_bytes, int32_t* status, void* stream);
 
+/* FP8 x FP8 product with one scale per operand: out[M,N] = (a[M,K] . b[N,K]^T) * scale_a * scale_b, a and b e4m3,
+ * scale_a / scale_b device pointers to ONE fp32 value each (NULL = 1), out bf16 or fp32 (out_dtype).  Stands in for
+ * tpudnnMatmulFp8Async behind aten::_scaled_mm on the reference device (native_ops/Scaled_mm.cpp:55-88; mat2 arrives
+ * as [N,K] there too, python/test/_scaled_mm.py:8).  Scales multiply, as in torch's own _scaled_mm; the reference's
+ * test only ever passes 1 (python/test/_scaled_mm.py:43-44).  K % 128 == 0, N % 64 == 0; tensor-core path only. */
+size_t b200moe_scaled_mm_workspace_bytes(int64_t M, int64_t K, int64_t N);
+int b200moe_scaled_mm(void* out, int out_dtype, const void* a, const void* b, const float* scale_a,
+                      const float* scale_b, int64_t M, int64_t K, int64_t N, void* workspace, size_t workspace_bytes,
+                      int32_t* status, void* stream);
+
 /* ---- expert parallelism over peer memory (NVLink) --------------------------------------------------
  * No reference counterpart (the reference has no expert parallelism).  One process per GPU of one node; every
  * rank allocates the same set of buffers, exports them (CUDA IPC) and imports its peers' handles, then builds

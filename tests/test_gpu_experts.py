@@ -85,20 +85,22 @@ def test_tcgen05_matches_simple_kernel_closely(m):
 
 
 @pytest.mark.parametrize("name", ["a", "b"])
-def test_w8a16_reference_arithmetic_small_golden(m, name):
+@pytest.mark.parametrize("impl", ["simple", "tcgen05"])
+def test_w8a16_reference_arithmetic_small_golden(m, name, impl):
     """W8A16 mode vs the outputs the REFERENCE's CPU code produced (bf16 scales, possibly negative)."""
     c = moe_small_case(name)
     d = to_dev(c)
     T, k = c["ids"].shape
     out = torch.empty(T, k, c["x"].shape[1], dtype=torch.bfloat16, device=DEV)
     m.ops.experts(out, d["x"], d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"],
-                  act_mode=m.lib.ACT_W8A16)
+                  act_mode=m.lib.ACT_W8A16, impl=m.lib.IMPL_SIMPLE if impl == "simple" else m.lib.IMPL_TCGEN05)
     r = _check(out, c["out"], "w8a16 vs reference golden")
     assert r["cos_sim"] > 0.99 and r["cos_diff"] < 1e-4, r
 
 
+@pytest.mark.parametrize("impl", ["simple", "tcgen05"])
 @pytest.mark.parametrize("shape", [(1, 7168, 256, 1, 1), (1, 7168, 256, 2, 2), (1, 7168, 256, 16, 8)])
-def test_w8a16_reference_shapes(m, shape):
+def test_w8a16_reference_shapes(m, shape, impl):
     """The reference's own parametrisation (test_moe.py:218-227), its seed, its acceptance thresholds."""
     T, H, I, E, k = shape
     z = load("moe_ref_shapes.npz")
@@ -106,9 +108,44 @@ def test_w8a16_reference_shapes(m, shape):
     want = bf16_from_bits(z["out_" + "_".join(map(str, shape))])
     out = torch.empty(T, k, H, dtype=torch.bfloat16, device=DEV)
     m.ops.experts(out, x.to(DEV), w0.to(DEV), w1.to(DEV), w2.transpose(1, 2).contiguous().to(DEV), s0.to(DEV),
-                  s1.to(DEV), s2.transpose(1, 2).contiguous().to(DEV), ids.to(DEV), act_mode=m.lib.ACT_W8A16)
+                  s1.to(DEV), s2.transpose(1, 2).contiguous().to(DEV), ids.to(DEV), act_mode=m.lib.ACT_W8A16,
+                  impl=m.lib.IMPL_SIMPLE if impl == "simple" else m.lib.IMPL_TCGEN05)
     r = _check(out, want, "w8a16 reference shape")
     assert r["cos_sim"] > 0.99 and r["cos_diff"] < 1e-4, r
+
+
+@pytest.mark.parametrize("T,H,I,E,k,shared", [(300, 1024, 512, 8, 2, False), (700, 384, 256, 5, 3, True),
+                                               (64, 2048, 768, 16, 4, False)])
+def test_w8a16_tensor_core_kernels_vs_oracle_a(m, T, H, I, E, k, shared):
+    """The W8A16 tensor-core kernels (weights dequantised to bf16 in shared memory, kind::f16 MMAs) on multi-tile
+    problems - several m-tiles per expert, H not a multiple of 256, K steps across scale blocks - against oracle-A,
+    the reference's CPU statements: per-slot and combined (+ shared expert) outputs, and against the CUDA-core twin."""
+    L = m.lib
+    p = small_problem(T, H, I, E, k, seed=T + 1)
+    want = O.experts_w8a16(p["x"], p["ids"], p["wg"], p["wu"], p["wd"], p["sg"], p["su"], p["sd"])
+    d = to_dev(p)
+    outs = {}
+    for impl in (L.IMPL_TCGEN05, L.IMPL_SIMPLE):
+        out = torch.full((T, k, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        m.ops.experts(out, d["x"], d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"],
+                      act_mode=L.ACT_W8A16, impl=impl, status=status)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.isfinite(out.float()).all(), "rows left unwritten"
+        outs[impl] = out
+    r = _check(outs[L.IMPL_TCGEN05], want, "w8a16 tcgen05 vs oracle-A")
+    assert r["cos_sim"] > 0.99 and r["cos_diff"] < 1e-4, r      # the reference's acceptance test
+    assert r["max_rel"] <= 8e-3, r                              # a bf16 rounding or two apart, not an FP8 step
+    _check(outs[L.IMPL_TCGEN05], outs[L.IMPL_SIMPLE], "w8a16 tcgen05 vs CUDA-core twin")
+    if shared:
+        sh = O.make_expert_weights(1, H, I, seed=123)
+        y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+        m.ops.experts(y, d["x"], d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"], d["w"],
+                      shared=tuple(t.to(DEV) for t in sh), act_mode=L.ACT_W8A16, impl=L.IMPL_TCGEN05)
+        ys = O.expert_mlp_w8a16(p["x"], *(t[0] for t in sh))
+        want_c = ((want.float() * p["w"].float()[..., None]).sum(1) + ys.float()).to(torch.bfloat16)
+        _check(y, want_c, "w8a16 tcgen05 combined + shared")
 
 
 def test_fp8_path_passes_reference_cos_sim_on_reference_inputs(m):

@@ -181,3 +181,24 @@ def test_mm_w8a16_dq_forward(m, M, K, N):
     assert met["max_rel"] <= 2e-2 and met["cosine"] >= 0.9995, met
     want_ref = x.float().double() @ wdq.double().T          # the reference's arithmetic: bf16 activations
     assert O.cos_sim(out.cpu().float().numpy(), want_ref.numpy()) > 0.99
+
+
+@pytest.mark.parametrize("M,K,N", [(500, 4096, 8192), (64, 512, 320), (1, 128, 64)])
+def test_scaled_mm_fp8(m, M, K, N):
+    """FP8 x FP8 product with one scale per operand, on the reference's own shape and input distribution
+    (python/test/_scaled_mm.py:39-44,80: uniform [-1,1] cast to e4m3, scales 1) plus non-trivial scales; expected value
+    = the fp32 product of the e4m3 values (every partial product is exact, so only fp32 summation order differs)."""
+    g = torch.Generator().manual_seed(1000)
+    x = (torch.rand(M, K, generator=g) * 2 - 1).to(torch.float8_e4m3fn)
+    y = (torch.rand(K, N, generator=g) * 2 - 1).to(torch.float8_e4m3fn)
+    want = x.float().double() @ y.float().double()
+    for sa, sb, dt in ((1.0, 1.0, torch.float32), (0.5, 3.0, torch.float32), (0.25, 2.0, torch.bfloat16)):
+        out = torch.ops.my_ops._scaled_mm(x.to(DEV), y.t().contiguous().to(DEV), torch.tensor(sa), torch.tensor(sb),
+                                          None, None, dt, False)
+        assert out.dtype == dt and tuple(out.shape) == (M, N)
+        met = O.parity_metrics(out.cpu(), want * sa * sb)
+        tol = 1e-5 if dt == torch.float32 else 4e-3
+        assert met["max_rel"] <= tol and met["cosine"] >= 0.99999, (sa, sb, dt, met)
+        # the reference's acceptance test: row-wise cosine >= 0.99 (python/test/_scaled_mm.py:62-65)
+        cs = torch.nn.functional.cosine_similarity(out.cpu().double(), want * sa * sb, dim=1)
+        assert float(cs.min()) >= 0.99

@@ -14,7 +14,8 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 NATIVE_LIB = os.path.join(HERE, "libb200moe.so")
 OPS_LIB = os.path.join(HERE, "libb200_moe_ops.so")
-CU_SOURCES = ["route.cu", "permute.cu", "gemm_simple.cu", "gemm_tc.cu", "experts.cu", "ep.cu", "ep_p2p.cu"]
+CU_SOURCES = ["route.cu", "permute.cu", "gemm_simple.cu", "gemm_tc.cu", "gemm_bf16_tc.cu", "experts.cu", "ep.cu",
+              "ep_p2p.cu"]
 NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
@@ -38,7 +39,7 @@ def _run(cmd, verbose):
 
 def build_native(force=False, verbose=False):
     srcs = [os.path.join(CSRC, s) for s in CU_SOURCES]
-    deps = srcs + [os.path.join(CSRC, h) for h in ("common.cuh", "internal.h")] + [
+    deps = srcs + [os.path.join(CSRC, h) for h in ("common.cuh", "internal.h", "tc_ptx.cuh")] + [
         os.path.join(ROOT, "include", "b200moe.h")]
     if not force and not _newer(NATIVE_LIB, deps):
         return NATIVE_LIB

@@ -51,7 +51,7 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   L.scratch = take(b200moe_permute_scratch_ints(P, d.E) * sizeof(int32_t));
   L.mtiles = take((size_t)L.max_mtiles * 2 * sizeof(int32_t));
   L.nmt = take(sizeof(int32_t));
-  L.xq = take(w8a8 ? (size_t)P * d.H : 0);
+  L.xq = take(w8a8 ? (size_t)P * d.H : (size_t)P * d.H * 2);  // W8A16: the bf16 rows of x gathered into sorted order
   L.xs = take(w8a8 ? nH * (size_t)L.ld * sizeof(float) : 0);
   L.hq = take(w8a8 ? (size_t)P * d.I : (size_t)P * d.I * 2);
   L.hs = take(w8a8 ? nI * (size_t)L.ld * sizeof(float) : 0);
@@ -130,7 +130,6 @@ int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_SHAPE(d->E <= 1024 && d->T * d->k < (1 << 24));
   MOE_CHECK_SHAPE(d->H < (1 << 24) && d->I < (1 << 24) && d->E * d->I < (int64_t(1) << 31));
   if (d->I_shared > 0) MOE_CHECK_ARG(d->out_mode != B200MOE_OUT_PER_SLOT);
-  if (d->impl == B200MOE_IMPL_TCGEN05) MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8);
   return B200MOE_OK;
 }
 
@@ -166,11 +165,16 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   auto I32 = [&](size_t off) { return reinterpret_cast<int32_t*>(ws + off); };
   const bool w8a8 = d->act_mode == B200MOE_ACT_W8A8;
   const bool use_tc = w8a8 && d->impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
-  if (d->impl == B200MOE_IMPL_TCGEN05 && !use_tc) return B200MOE_EDRIVER;
+  // W8A16 (the reference's arithmetic) has its own tensor-core kernels: bf16 x bf16 with the weights dequantised in
+  // shared memory
+  const bool use_tc16 = !w8a8 && d->impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
+  if (d->impl == B200MOE_IMPL_TCGEN05 && !use_tc && !use_tc16) return B200MOE_EDRIVER;
   const bool combined = d->out_mode != B200MOE_OUT_PER_SLOT;
   // per-GEMM kernel family (A/B tests), else the call's
   const bool tc1 = w8a8 && moe_tc_available() && (d->impl_gate_up ? d->impl_gate_up == B200MOE_IMPL_TCGEN05 : use_tc);
   const bool tc2 = w8a8 && moe_tc_available() && (d->impl_down ? d->impl_down == B200MOE_IMPL_TCGEN05 : use_tc);
+  const bool tc1_16 = !w8a8 && moe_tc_available() && (d->impl_gate_up ? d->impl_gate_up == B200MOE_IMPL_TCGEN05 : use_tc16);
+  const bool tc2_16 = !w8a8 && moe_tc_available() && (d->impl_down ? d->impl_down == B200MOE_IMPL_TCGEN05 : use_tc16);
   // the fused combine lives in the tensor-core down GEMM's epilogue; other paths combine with the separate kernel
   const bool fused = d->out_mode == B200MOE_OUT_COMBINED_FUSED && tc2;
   // a stage may be re-run alone on a workspace that a whole call of the same sizes has filled
@@ -240,11 +244,20 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g.hs_t = reinterpret_cast<float*>(ws + L.hs);
   g.h16 = reinterpret_cast<__nv_bfloat16*>(ws + L.hq);
   g.status = status;
+  __nv_bfloat16* xg = reinterpret_cast<__nv_bfloat16*>(ws + L.xq);  // W8A16 tensor-core path: x rows in sorted order
+  if (tc1_16 && do_prep) {
+    rc = moe_gather_rows_bf16(xg, reinterpret_cast<const __nv_bfloat16*>(x), I32(L.sorted), (int)d->k, L.P, (int)d->H, st);
+    if (rc) return rc;
+  }
   if (do_g1) {
     if (tc1) {
       MoeGemmArgs t = g;
       if (cvt) t.s0 = sc32, t.s1 = sc32 + nsc, t.scale_dtype = B200MOE_F32;
       rc = moe_gemm1_tc(t, st);
+    } else if (tc1_16) {
+      MoeGemmArgs t = g;
+      t.a16 = xg;
+      rc = moe_gemm1_w8a16_tc(t, st);
     } else {
       rc = moe_gemm1_simple(g, d->act_mode, st);
     }
@@ -275,6 +288,8 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
       }
       rc = moe_gemm2_tc(t, st);
       if (!rc && !fused && t.ksplit > 1) rc = moe_f32_rows_to_bf16(g2.out, t.out32, L.P * d->H, st);
+    } else if (tc2_16) {
+      rc = moe_gemm2_w8a16_tc(g2, st);
     } else {
       rc = moe_gemm2_simple(g2, d->act_mode, st);
     }
@@ -330,6 +345,8 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
         MoeGemmArgs t = s;
         if (cvt) t.s0 = ssc32, t.s1 = ssc32 + nscs, t.scale_dtype = B200MOE_F32;
         rc = moe_gemm1_tc(t, ss);
+      } else if (tc1_16) {
+        rc = moe_gemm1_w8a16_tc(s, ss);   // identity rows: x itself is the A operand
       } else {
         rc = moe_gemm1_simple(s, d->act_mode, ss);
       }
@@ -359,6 +376,8 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
         }
         rc = moe_gemm2_tc(t, ss);
         if (!rc && !fused && t.ksplit > 1) rc = moe_f32_rows_to_bf16(s2.out, t.out32, d->T * d->H, ss);
+      } else if (tc2_16) {
+        rc = moe_gemm2_w8a16_tc(s2, ss);
       } else {
         rc = moe_gemm2_simple(s2, d->act_mode, ss);
       }
@@ -601,6 +620,93 @@ extern "C" int b200moe_linear_w8(void* out, const void* x, const void* w, const 
   g.I = (int)N;
   g.E = 1;
   g.out = reinterpret_cast<__nv_bfloat16*>(out);
+  g.status = status;
+  return moe_linear_tc(g, st);
+}
+
+// ---- FP8 x FP8 matrix product with one scale per operand ------------------------------------------------------------
+namespace {
+__global__ void fill_scalar_scale_kernel(float* __restrict__ dst, const float* __restrict__ scale, int64_t n) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = scale ? *scale : 1.0f;
+}
+struct SmmLayout {
+  size_t offsets, mtiles, nmt, xs, ws, total;
+  int64_t ld;
+  int max_mtiles;
+};
+SmmLayout smm_layout(int64_t M, int64_t K, int64_t N) {
+  SmmLayout L{};
+  size_t o = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = o;
+    o = (o + bytes + 255) & ~(size_t)255;
+    return at;
+  };
+  L.ld = (M + kTileM - 1) / kTileM * kTileM;
+  if (L.ld == 0) L.ld = kTileM;
+  L.max_mtiles = (int)(L.ld / kTileM);
+  L.offsets = take(2 * sizeof(int32_t));
+  L.mtiles = take((size_t)L.max_mtiles * 2 * sizeof(int32_t));
+  L.nmt = take(sizeof(int32_t));
+  L.xs = take((size_t)(K / kBlock) * L.ld * sizeof(float));
+  L.ws = take((size_t)((N + kBlock - 1) / kBlock) * (K / kBlock) * sizeof(float));
+  L.total = o;
+  return L;
+}
+}  // namespace
+
+extern "C" size_t b200moe_scaled_mm_workspace_bytes(int64_t M, int64_t K, int64_t N) {
+  if (M < 0 || K <= 0 || N <= 0 || K % kBlock || N % 64) return 0;
+  return smm_layout(M, K, N).total;
+}
+
+extern "C" int b200moe_scaled_mm(void* out, int out_dtype, const void* a, const void* b, const float* scale_a,
+                                 const float* scale_b, int64_t M, int64_t K, int64_t N, void* workspace,
+                                 size_t workspace_bytes, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(M >= 0 && K > 0 && N > 0);
+  MOE_CHECK_ARG(out_dtype == B200MOE_BF16 || out_dtype == B200MOE_F32);
+  MOE_CHECK_SHAPE(K % kBlock == 0 && N % 64 == 0 && M < (1 << 24) && N < (int64_t(1) << 31));
+  if (M == 0) return B200MOE_OK;
+  MOE_CHECK_ARG(out && a && b);
+  if (!moe_aligned16(out) || !moe_aligned16(a) || !moe_aligned16(b)) return B200MOE_EALIGN;
+  if (!moe_tc_available()) return B200MOE_EDRIVER;
+  const SmmLayout L = smm_layout(M, K, N);
+  if (!workspace || workspace_bytes < L.total || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return B200MOE_EWORKSPACE;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = reinterpret_cast<char*>(workspace);
+  int32_t* offsets = reinterpret_cast<int32_t*>(ws + L.offsets);
+  int32_t* mtiles = reinterpret_cast<int32_t*>(ws + L.mtiles);
+  int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
+  int rc = moe_fill_identity_offsets(offsets, M, st);
+  if (rc) return rc;
+  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, st);
+  if (rc) return rc;
+  // the kernel applies act_scale[row,kb] * weight_scale[nb,kb] to every 128-deep partial sum: constant grids here
+  const int64_t nxs = (K / kBlock) * L.ld, nws = ((N + kBlock - 1) / kBlock) * (K / kBlock);
+  fill_scalar_scale_kernel<<<(unsigned)((nxs + 255) / 256), 256, 0, st>>>(reinterpret_cast<float*>(ws + L.xs), scale_a, nxs);
+  fill_scalar_scale_kernel<<<(unsigned)((nws + 255) / 256), 256, 0, st>>>(reinterpret_cast<float*>(ws + L.ws), scale_b, nws);
+  rc = moe_launch_status();
+  if (rc) return rc;
+  MoeGemmArgs g{};
+  g.aq = reinterpret_cast<const uint8_t*>(a);
+  g.as_t = reinterpret_cast<const float*>(ws + L.xs);
+  g.ld = L.ld;
+  g.div = 1;
+  g.w0 = reinterpret_cast<const uint8_t*>(b);
+  g.s0 = ws + L.ws;
+  g.scale_dtype = B200MOE_F32;
+  g.mtiles = mtiles;
+  g.num_mtiles = nmt;
+  g.offsets = offsets;
+  g.max_mtiles = L.max_mtiles;
+  g.P = M;
+  g.H = (int)K;
+  g.I = (int)N;
+  g.E = 1;
+  if (out_dtype == B200MOE_F32) g.out32 = reinterpret_cast<float*>(out);
+  else g.out = reinterpret_cast<__nv_bfloat16*>(out);
   g.status = status;
   return moe_linear_tc(g, st);
 }

@@ -21,10 +21,7 @@
 //
 // No multicast loads anywhere.  Every wait is bounded: on a time-out the CTA raises status bit 1, all roles
 // leave their loops, tensor memory is released and the kernel returns.
-#include <cuda.h>
-#include <stdlib.h>
-
-#include "internal.h"
+#include "tc_ptx.cuh"
 
 namespace {
 
@@ -54,7 +51,6 @@ constexpr int TC_A_BYTES = 128 * 128;       // 128 rows x 128 B
 constexpr int TC_B_BYTES = 2 * 128 * 128;   // two 128 x 128 B boxes
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr int TC_TMEM_COLS = 512;           // two accumulator buffers of 256 fp32 columns
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 19;  // polls (each up to MOE_TC_HINT ns, then with back-off) before a wait gives up: ~1 s
 
 struct TcShared {
   uint64_t full[TC_STAGES];
@@ -84,7 +80,7 @@ struct TcArgs {
   int H, I, NT;
   int KS;        // K splits (down GEMM of decode-size batches); 1 = none
   int m_major;   // work-item order: 0 = n-tile slow, m-tile fast; 1 = m-tile slow, n-tile fast (see launch_tc)
-  float* out32;  // fp32 accumulation target when KS > 1
+  float* out32;  // fp32 accumulation target when KS > 1; with KS == 1 (linear layer only): fp32 rows stored instead of bf16
   // down GEMM with the weighted combine fused in: row r adds comb_w[pair] * y[r,:] into comb32[pair / div, :] (fp32,
   // red.global.add; pair = row_map[r] or r, comb_w NULL = weight 1); overrides out / out32
   float* comb32;
@@ -96,118 +92,6 @@ struct TcArgs {
   int32_t* status;
 };
 
-// ---- PTX wrappers ----------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-#ifndef MOE_TC_ABL
-#define MOE_TC_ABL 0
-#endif
-#ifndef MOE_TC_PIPE
-#define MOE_TC_PIPE 2
-#endif
-#ifndef MOE_TC_HINT
-#define MOE_TC_HINT 2000
-#endif
-// One poll.  With a suspend-time hint (ns) the thread sleeps in hardware until the phase completes or the hint runs
-// out, instead of coming back at once: fewer issue slots and shared-memory operations taken from the epilogue warps.
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-#if MOE_TC_HINT > 0
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"((uint32_t)MOE_TC_HINT)
-      : "memory");
-#else
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-#endif
-  return ok;
-}
-// non-blocking test of a phase
-__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait.  Returns false when it gave up or another role already did.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 4096) __nanosleep(128);
-    if ((i & 255) == 255) {
-      if (*abort_flag) return false;
-      if (i > TC_SPIN_LIMIT) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread.
-// issue only; the destination registers are valid after tc_ld_wait16x2 on them
-__device__ __forceinline__ void tc_ld_issue(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-// wait for every outstanding tcgen05.ld; the two register sets are in/out operands so that no use of them can be
-// scheduled above the wait
-__device__ __forceinline__ void tc_ld_wait(uint32_t (&a)[16], uint32_t (&b)[16]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(a[0]), "+r"(a[1]), "+r"(a[2]), "+r"(a[3]), "+r"(a[4]), "+r"(a[5]), "+r"(a[6]), "+r"(a[7]),
-                 "+r"(a[8]), "+r"(a[9]), "+r"(a[10]), "+r"(a[11]), "+r"(a[12]), "+r"(a[13]), "+r"(a[14]), "+r"(a[15]),
-                 "+r"(b[0]), "+r"(b[1]), "+r"(b[2]), "+r"(b[3]), "+r"(b[4]), "+r"(b[5]), "+r"(b[6]), "+r"(b[7]),
-                 "+r"(b[8]), "+r"(b[9]), "+r"(b[10]), "+r"(b[11]), "+r"(b[12]), "+r"(b[13]), "+r"(b[14]), "+r"(b[15])
-               :
-               : "memory");
-}
 // A pair of fp32 accumulators.  Two forms: one fma.rn.f32x2 per pair (half the instruction slots) or two scalar
 // FMAs (MOE_TC_SCALAR_FMA; the form the TMEM-read microbenchmark found a little faster on this part).
 #ifndef MOE_TC_SCALAR_FMA
@@ -256,15 +140,6 @@ __device__ __forceinline__ float moe_silu_fast(float x) {
   return fmaf(hx, t, hx);
 }
 
-// Shared-memory matrix descriptor of a 128-byte-swizzled operand tile (8-row x 128-byte atoms, 1024 B each).
-//   K-major : rows are M/N indices, 128 B of K per row; SBO = 1024 (next 8 rows); LBO unused (1)
-//   MN-major: rows are K indices, 128 B of M/N per row; SBO = 1024 (next 8 K rows); LBO = distance between
-//             128-wide M/N chunks
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) /*descriptor version of sm_100*/ |
-         (2ull << 61) /*128-byte swizzle*/;
-}
 // Instruction descriptor, kind::f8f6f4: D fp32, A/B e4m3, M = 128, N = 256
 __host__ __device__ constexpr uint32_t make_idesc(int b_mn_major) {
   return (1u << 4) | ((uint32_t)b_mn_major << 16) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
@@ -683,6 +558,13 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                            "f"(p1.x), "f"(p1.y)
                            : "memory");
             }
+          } else if (col < OUTW && DENSE && a.out32) {  // fp32 output rows (plain stores)
+            float4* dst = reinterpret_cast<float4*>(a.out32 + dstrow * OUTW + col);
+#pragma unroll
+            for (int v4 = 0; v4 < TC_CW / 4; ++v4) {
+              const float2 p0 = unpack2(acc[j][v4 * 2]), p1 = unpack2(acc[j][v4 * 2 + 1]);
+              dst[v4] = make_float4(p0.x, p0.y, p1.x, p1.y);
+            }
           } else if (col < OUTW) {
             uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * OUTW + col);
 #pragma unroll
@@ -718,22 +600,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 }
 
 // ---- host side ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
 // row-major u8 matrix [rows, cols], box 128 x 128 bytes, 128-byte swizzle, zero fill outside
 bool make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
   EncodeTiledFn enc = get_encode_fn();

@@ -55,6 +55,11 @@ int moe_gemm1_tc(const MoeGemmArgs& a, cudaStream_t st);
 int moe_gemm2_tc(const MoeGemmArgs& a, cudaStream_t st);
 // plain linear layer: out[r, :I] = A[r, :H] * w0^T, w0 [E*I, H] K-major with scales s0 [E, ceil(I/128), H/128]; bf16 rows of I
 int moe_linear_tc(const MoeGemmArgs& a, cudaStream_t st);
+// the reference arithmetic (bf16 activations, weights dequantised to bf16) on the tensor cores; a16 = rows in sorted order
+int moe_gemm1_w8a16_tc(const MoeGemmArgs& a, cudaStream_t st);
+int moe_gemm2_w8a16_tc(const MoeGemmArgs& a, cudaStream_t st);
+int moe_gather_rows_bf16(__nv_bfloat16* dst, const __nv_bfloat16* x, const int32_t* row_map, int div, int64_t rows,
+                         int H, cudaStream_t st);
 int moe_f32_rows_to_bf16(__nv_bfloat16* out, const float* in, int64_t n, cudaStream_t st);
 int moe_device_sm_count();
 bool moe_tc_available();

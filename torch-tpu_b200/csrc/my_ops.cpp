@@ -392,6 +392,43 @@ Tensor mm_w8a16_dq_forward(Tensor& input, Tensor& weight, Tensor& scale, Tensor&
   return output;
 }
 
+// aten::_scaled_mm as the reference implements it on its device (native_ops/Scaled_mm.cpp:55-88 -> tpudnnMatmulFp8Async):
+// self [M,K] and mat2 [N,K] float8_e4m3fn (the reference's caller passes the transposed, contiguous second operand,
+// python/test/_scaled_mm.py:8), one fp32 scale per operand, result [M,N] in out_dtype (bf16 or fp32; default bf16).
+// Registered under my_ops because on CUDA aten::_scaled_mm already belongs to PyTorch; argument order as in the
+// reference's wrapper.  bias and scale_result are not supported (None in the reference's test).
+Tensor scaled_mm_fp8(const Tensor& self, const Tensor& mat2, const Tensor& scale_a, const Tensor& scale_b,
+                     const c10::optional<Tensor>& bias, const c10::optional<Tensor>& scale_result,
+                     c10::optional<ScalarType> out_dtype, bool use_fast_accum) {
+  (void)use_fast_accum;
+  check_cuda_contig(self, "self");
+  check_cuda_contig(mat2, "mat2");
+  TORCH_CHECK(self.dim() == 2, "self must be a matrix");
+  TORCH_CHECK(mat2.dim() == 2, "mat2 must be a matrix");
+  TORCH_CHECK(self.scalar_type() == kFloat8_e4m3fn && mat2.scalar_type() == kFloat8_e4m3fn,
+              "self and mat2 must be float8_e4m3fn");
+  TORCH_CHECK(self.size(1) == mat2.size(1), "self [M,K] and mat2 [N,K] must share K");
+  TORCH_CHECK(!bias.has_value() && !scale_result.has_value(), "bias / scale_result are not supported (pass None)");
+  TORCH_CHECK(scale_a.numel() == 1 && scale_b.numel() == 1, "scale_a and scale_b must hold one value each");
+  const ScalarType odt = out_dtype.value_or(kBFloat16);
+  TORCH_CHECK(odt == kBFloat16 || odt == kFloat, "out_dtype must be bfloat16 or float32");
+  const int64_t M = self.size(0), K = self.size(1), N = mat2.size(0);
+  c10::cuda::CUDAGuard guard(self.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  Tensor sa = scale_a.to(self.device(), kFloat).contiguous(), sb = scale_b.to(self.device(), kFloat).contiguous();
+  Tensor out = at::empty({M, N}, self.options().dtype(odt));   // the reference allocates its result too (:118)
+  const size_t need = b200moe_scaled_mm_workspace_bytes(M, K, N);
+  TORCH_CHECK(need > 0 || M == 0, "_scaled_mm: unsupported sizes (K % 128 == 0 and N % 64 == 0 required)");
+  Tensor ws = workspace_for(self.device(), st, need);
+  void* wsp = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 255) & ~uintptr_t(255));
+  const size_t ws_bytes = (size_t)ws.numel() - (reinterpret_cast<char*>(wsp) - reinterpret_cast<char*>(ws.data_ptr()));
+  check_rc(b200moe_scaled_mm(out.data_ptr(), odt == kFloat ? B200MOE_F32 : B200MOE_BF16, self.data_ptr(),
+                             mat2.data_ptr(), sa.data_ptr<float>(), sb.data_ptr<float>(), M, K, N, wsp, ws_bytes,
+                             nullptr, st),
+           "b200moe_scaled_mm");
+  return out;
+}
+
 // The device status word of the current device (int32 [1]; bits in include/b200moe.h).  Not part of the reference's
 // surface: the reference reports device errors through its runtime, this library through that word.
 Tensor b200_moe_status() {
@@ -400,6 +437,7 @@ Tensor b200_moe_status() {
 
 TORCH_LIBRARY(my_ops, m) {
   m.def("b200_moe_status", b200_moe_status);
+  m.def("_scaled_mm", scaled_mm_fp8);
   m.def("fused_moe_grouped_topk", fused_moe_grouped_topk);
   m.def("fused_moe_fused_experts", fused_moe_fused_experts);
   m.def("fused_moe_fused_experts_v2", fused_moe_fused_experts_v2);

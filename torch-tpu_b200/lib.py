@@ -67,6 +67,9 @@ SIGNATURES = {
     "b200moe_linear_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int]),
     "b200moe_linear_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p,
                                   c_size_t, c_void_p, c_void_p]),
+    "b200moe_scaled_mm_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "b200moe_scaled_mm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                  c_void_p, c_size_t, c_void_p, c_void_p]),
     "b200moe_p2p_alloc": (c_int, [POINTER(c_void_p), c_size_t]),
     "b200moe_p2p_free": (c_int, [c_void_p]),
     "b200moe_p2p_export": (c_int, [c_char_p, c_void_p]),
