@@ -156,8 +156,8 @@ int b200moe_quant_rows(uint8_t* q, float* s_t, int64_t ld, const void* x, const 
  *
  *   x        bf16 [T,H]
  *   w_gate, w_up, w_down   e4m3 [E,I,H]  (down = W_down^T, contiguous: test_moe.py:285)
- *   s_gate, s_up, s_down   [E, I/128, H/128] of scale_dtype (fp32 or bf16); NULL with
- *                          scale_dtype = -1 is not supported here (bf16 weights are out of scope)
+ *   s_gate, s_up, s_down   [E, I/128, H/128] of scale_dtype (fp32 or bf16); ignored (may be NULL) with
+ *                          weights_bf16 = 1, where the three weight tensors are bf16
  *   ids      int32 [T,k];  topk_w  [T,k] of w_dtype (needed for B200MOE_OUT_COMBINED, else may be NULL)
  *   shared_* optional dense expert applied to every token with weight 1 (combined mode only), same
  *            layouts with E = 1 and intermediate size I_shared; pass NULL / 0 to disable
@@ -175,6 +175,9 @@ typedef struct {
   int w_dtype;        /* dtype of topk_w: B200MOE_F32 | B200MOE_BF16 */
   int impl_gate_up;   /* B200MOE_IMPL_AUTO = follow `impl`; else the kernel family of the gate/up GEMM alone */
   int impl_down;      /* the same for the down GEMM (tests A/B one GEMM at a time with these two) */
+  int weights_bf16;   /* 0 = e4m3 weights with block scales.  1 = bf16 weights [E,I,H] without scales (the reference op
+                         called with scales = None, python/test/fused_moe_bf16.py:113-122): scale pointers are
+                         ignored, act_mode must be B200MOE_ACT_W8A16, tensor-core path only */
   int stages;         /* 0 = the whole call.  Else a mask of B200MOE_STAGE_*: only those stages are enqueued, on
                          a workspace that a whole call with the same sizes and inputs has filled before (how a
                          benchmark times one GEMM alone).  Any other bit is rejected. */
@@ -264,7 +267,8 @@ int b200moe_scaled_mm(void* out, int out_dtype, const void* a, const void* b, co
  * at start, one per rank): the barrier then uses counter + 1 and advances the counter itself, so the launches carry
  * no per-call value and a whole layer call can be captured into a CUDA graph and replayed.
  *
- * Buffers of one rank, for capacity C rows (C >= the most rows the rank can receive, e.g. N*T*k):
+ * Buffers of one rank, for capacity C rows (C >= the most rows the rank can receive, e.g. N*T*k; with a smaller C the
+ * rows that do not fit are dropped by dispatch - status bit 3 - and every later kernel clips its row ranges to C):
  *   flags   uint32 [8]            zero at start            cnt    int32 [N][E]
  *   xq      u8 [C][H]             xs_rows f32 [C][H/128]              src   int32 [C]   (written by the peers)
  *   xs_t    f32 [H/128][ld], ld >= C      (local: the scales in the layout the GEMMs read)

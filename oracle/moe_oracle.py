@@ -268,6 +268,31 @@ def experts_w8a16(x, ids, wg, wu, wd, sg, su, sd, dtype: torch.dtype = torch.bfl
     return out
 
 
+def experts_bf16(x, ids, wg, wu, wd_ih, per_token: bool = False) -> torch.Tensor:
+    """bf16-weight experts, un-weighted ``[T,k,H]``: ``QwenMlp.forward`` / ``QwenMoE.forward``
+    (python/test/fused_moe_bf16.py:63-95) - gate linear, SiLU, up linear, multiply, down linear, all in bf16.
+    ``wd_ih`` is the op's layout ``[E,I,H]`` (the transposed, contiguous down projection, :178) and is transposed
+    back so that the same ``F.linear`` call runs.  ``per_token`` walks the pairs as the reference does."""
+    T, k = ids.shape
+    H = x.shape[1]
+    x = x.to(torch.bfloat16)
+    out = torch.zeros(T, k, H, dtype=torch.bfloat16)
+
+    def mlp(rows, e):
+        a = F.silu(F.linear(rows, wg[e]))
+        return F.linear(a * F.linear(rows, wu[e]), wd_ih[e].t().contiguous())
+    if per_token:
+        for t in range(T):
+            for j in range(k):
+                out[t, j, :] = mlp(x[t], int(ids[t, j]))
+        return out
+    flat = ids.reshape(-1).to(torch.int64)
+    for e in torch.unique(flat).tolist():
+        pos = torch.nonzero(flat == e).flatten()
+        out.view(T * k, H)[pos] = mlp(x[pos // k], e)
+    return out
+
+
 def expert_mlp_w8a8(x: torch.Tensor, wg, wu, wd_ih, sg, su, sd_ih) -> torch.Tensor:
     """One expert under the W8A8 contract, fp32 arithmetic: the statements of
     ``DeepseekMlp.forward`` (test_moe.py:63-84) with ``x`` and the SwiGLU product each replaced

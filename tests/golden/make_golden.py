@@ -21,6 +21,8 @@ What is recorded:
                     (test_moe.py:218-227) with inputs regenerated from seed 1000 by
                     ``ref_moe_inputs`` below (the statements of test_moe.py:251-274).
   mlp_dense.npz   - ``mlp_w8a16_dq_cpu`` (test_mlp_w8a16_dq.py:53-85) on a small stored case.
+  moe_bf16.npz    - ``QwenMoE`` (python/test/fused_moe_bf16.py:63-95: bf16 weights, no scales) on small stored inputs
+                    built the way fused_moe_bf16.py:152-167 builds them (randn bf16 weights, distinct experts).
 """
 import importlib.util
 import os
@@ -161,6 +163,23 @@ def main(ref_root: str) -> None:
     o = RD.mlp_w8a16_dq_cpu(x, wg, wu, wd, sg, su, sd, 128)
     np.savez_compressed(os.path.join(HERE, "mlp_dense.npz"), x=_bits(x), wg=_bits(wg), wu=_bits(wu),
                         wd=_bits(wd), sg=_bits(sg), su=_bits(su), sd=_bits(sd), out=o.numpy())
+    # ---- bf16-weight experts ---------------------------------------------------------------
+    sys.path.insert(0, os.path.join(ref_root, "python/test"))
+    import fused_moe_bf16 as RB      # noqa: E402
+    torch.manual_seed(11)
+    random.seed(11)
+    cases = {}
+    for name, (T, H, I, E, k) in {"a": (6, 256, 128, 4, 2), "b": (3, 384, 128, 2, 2)}.items():
+        ids = torch.tensor([random.sample(range(E), k) for _ in range(T)], dtype=torch.int32)
+        w0 = torch.randn(E, I, H).to(torch.bfloat16)
+        w1 = torch.randn(E, I, H).to(torch.bfloat16)
+        w2 = torch.randn(E, H, I).to(torch.bfloat16)
+        x = torch.randn(T, H).to(torch.bfloat16)
+        o = RB.QwenMoE(E, k, w0, w1, w2)(x, ids)
+        for key, t in (("x", x), ("w0", w0), ("w1", w1), ("w2", w2), ("out", o)):
+            cases[f"{name}_{key}"] = _bits(t)
+        cases[f"{name}_ids"] = ids.numpy()
+    np.savez_compressed(os.path.join(HERE, "moe_bf16.npz"), **cases)
     print("golden fixtures written to", HERE)
 
 

@@ -174,3 +174,47 @@ def test_empty_batch_and_bad_arguments(m):
         m.ops.experts(torch.empty(4, 2, 192, dtype=torch.bfloat16, device=DEV), p["x"][:, :192].contiguous(),
                       p["wg"][:, :, :192].contiguous(), p["wu"][:, :, :192].contiguous(),
                       p["wd"][:, :, :192].contiguous(), p["sg"], p["su"], p["sd"], p["ids"])
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_bf16_weight_experts_reference_golden(m, name):
+    """bf16 weights without scales (the reference op called with scales = None, python/test/fused_moe_bf16.py:113-122)
+    against the outputs of the reference's own CPU class, with its acceptance threshold cos_diff < 1e-4 (:191)."""
+    z = load("moe_bf16.npz")
+    x, w0, w1, w2, want = (bf16_from_bits(z[f"{name}_{k}"]) for k in ("x", "w0", "w1", "w2", "out"))
+    ids = torch.from_numpy(z[f"{name}_ids"].copy())
+    T, k = ids.shape
+    H = x.shape[1]
+    wd = w2.transpose(1, 2).contiguous()
+    out = torch.full((T, k, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    m.ops.experts(out, x.to(DEV), w0.to(DEV), w1.to(DEV), wd.to(DEV), None, None, None, ids.to(DEV))
+    r = _check(out, want, "bf16-weight experts vs reference golden")
+    assert r["cos_diff"] < 1e-4, r
+    # through the reference-facing op, scales = None
+    m.load_ops()
+    out2 = torch.zeros(T, k, H, dtype=torch.bfloat16, device=DEV)
+    rw = torch.ones(T, k, dtype=torch.bfloat16, device=DEV)
+    torch.ops.my_ops.fused_moe_fused_experts(out2, x.to(DEV), None, None, w0.to(DEV), w1.to(DEV), wd.to(DEV), None,
+                                             None, None, ids.to(DEV), rw, None, None, None, 128, w0.shape[0], k, False,
+                                             1, 1, None, None, None, False)
+    assert torch.equal(out2, out)
+
+
+def test_bf16_weight_experts_multi_tile(m):
+    """Several m-tiles per expert, H not a multiple of 256, combined output: against the oracle's batched form."""
+    T, H, I, E, k = 400, 384, 256, 4, 2
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    w0, w1 = ((torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16) for _ in range(2))
+    wd = (torch.randn(E, I, H, generator=g) * 0.05).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, k, generator=g) + 0.1
+    want = O.experts_bf16(x, ids, w0, w1, wd)
+    out = torch.full((T, k, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+    m.ops.experts(out, x.to(DEV), w0.to(DEV), w1.to(DEV), wd.to(DEV), None, None, None, ids.to(DEV))
+    assert torch.isfinite(out.float()).all()
+    r = _check(out, want, "bf16-weight experts, multi-tile")
+    assert r["cos_diff"] < 1e-4 and r["max_rel"] <= 8e-3, r
+    y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    m.ops.experts(y, x.to(DEV), w0.to(DEV), w1.to(DEV), wd.to(DEV), None, None, None, ids.to(DEV), w.to(DEV))
+    _check(y, (want.float() * w[..., None]).sum(1), "bf16-weight experts, combined")

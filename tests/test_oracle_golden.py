@@ -132,3 +132,16 @@ def test_route_oracles_basic():
     assert ((ids2 // 8).unique(dim=-1).shape[-1]) <= 6
     for r in range(32):
         assert len(set((ids2[r] // 8).tolist())) <= 4
+
+
+@pytest.mark.parametrize("name", ["a", "b"])
+def test_experts_bf16_matches_reference(name):
+    """bf16-weight experts: the oracle's restatement of QwenMoE (python/test/fused_moe_bf16.py:63-95) against the
+    outputs of the reference's own class, walking the pairs as it does: bit for bit."""
+    z = load("moe_bf16.npz")
+    x, w0, w1, w2, out = (bf16_from_bits(z[f"{name}_{k}"]) for k in ("x", "w0", "w1", "w2", "out"))
+    ids = torch.from_numpy(z[f"{name}_ids"].copy())
+    wd = w2.transpose(1, 2).contiguous()                     # the op's layout (fused_moe_bf16.py:178)
+    assert torch.equal(O.experts_bf16(x, ids, w0, w1, wd, per_token=True), out)
+    m = O.parity_metrics(O.experts_bf16(x, ids, w0, w1, wd), out)   # batched per expert: a bf16 ulp at most
+    assert m["max_rel"] < 8e-3 and m["cosine"] > 0.99999, m

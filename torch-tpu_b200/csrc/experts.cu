@@ -122,6 +122,10 @@ int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_ARG(d->impl_gate_up >= B200MOE_IMPL_AUTO && d->impl_gate_up <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG(d->impl_down >= B200MOE_IMPL_AUTO && d->impl_down <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG((d->stages & ~B200MOE_STAGE_ALL) == 0);
+  MOE_CHECK_ARG(d->weights_bf16 == 0 || d->weights_bf16 == 1);
+  if (d->weights_bf16)
+    MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A16 && d->impl != B200MOE_IMPL_SIMPLE &&
+                  d->impl_gate_up != B200MOE_IMPL_SIMPLE && d->impl_down != B200MOE_IMPL_SIMPLE);
   MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A8 || d->act_mode == B200MOE_ACT_W8A16);
   MOE_CHECK_ARG(d->impl >= B200MOE_IMPL_AUTO && d->impl <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG(d->scale_dtype == B200MOE_F32 || d->scale_dtype == B200MOE_BF16);
@@ -150,10 +154,12 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   int rc = check_desc(d);
   if (rc != B200MOE_OK) return rc;
   if (d->T == 0) return B200MOE_OK;  // nothing to do; empty tensors may carry null pointers
-  MOE_CHECK_ARG(out && x && w_gate && w_up && w_down && s_gate && s_up && s_down && ids);
+  MOE_CHECK_ARG(out && x && w_gate && w_up && w_down && ids);
+  if (!d->weights_bf16) MOE_CHECK_ARG(s_gate && s_up && s_down);
   if (d->out_mode != B200MOE_OUT_PER_SLOT) MOE_CHECK_ARG(topk_w);
   if (d->I_shared > 0)
-    MOE_CHECK_ARG(shared_w_gate && shared_w_up && shared_w_down && shared_s_gate && shared_s_up && shared_s_down);
+    MOE_CHECK_ARG(shared_w_gate && shared_w_up && shared_w_down &&
+                  (d->weights_bf16 || (shared_s_gate && shared_s_up && shared_s_down)));
   if (!moe_aligned16(out) || !moe_aligned16(x) || !moe_aligned16(w_gate) || !moe_aligned16(w_up) ||
       !moe_aligned16(w_down))
     return B200MOE_EALIGN;
@@ -169,6 +175,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   // shared memory
   const bool use_tc16 = !w8a8 && d->impl != B200MOE_IMPL_SIMPLE && moe_tc_available();
   if (d->impl == B200MOE_IMPL_TCGEN05 && !use_tc && !use_tc16) return B200MOE_EDRIVER;
+  if (d->weights_bf16 && !use_tc16) return B200MOE_EDRIVER;  // bf16 weights exist on the tensor-core path only
   const bool combined = d->out_mode != B200MOE_OUT_PER_SLOT;
   // per-GEMM kernel family (A/B tests), else the call's
   const bool tc1 = w8a8 && moe_tc_available() && (d->impl_gate_up ? d->impl_gate_up == B200MOE_IMPL_TCGEN05 : use_tc);
@@ -200,7 +207,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   if (do_prep) {
     rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
     if (rc) return rc;
-    rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, st);
+    rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, L.P, L.max_mtiles, st);
     if (rc) return rc;
   }
   if (w8a8 && do_prep) {
@@ -232,6 +239,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g.s0 = s_gate;
   g.s1 = s_up;
   g.scale_dtype = d->scale_dtype;
+  g.w_bf16 = d->weights_bf16;
   g.mtiles = I32(L.mtiles);
   g.num_mtiles = I32(L.nmt);
   g.offsets = I32(L.offsets);
@@ -302,7 +310,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     if (do_prep) {
       rc = moe_fill_identity_offsets(I32(L.s_offsets), d->T, ss);
       if (rc) return rc;
-      rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, ss);
+      rc = moe_build_mtiles(I32(L.s_mtiles), I32(L.s_nmt), I32(L.s_offsets), 1, d->T, L.s_max_mtiles, ss);
       if (rc) return rc;
     }
     if (w8a8 && do_prep) {
@@ -456,7 +464,7 @@ int grouped_mlp_impl(void* y, const uint8_t* xq, const float* xs_t, int64_t ld, 
   if (row_src && !use_tc) return B200MOE_EDRIVER;  // peer output exists on the tensor-core path only
   int32_t* mtiles = reinterpret_cast<int32_t*>(ws + L.mtiles);
   int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
-  int rc = moe_build_mtiles(mtiles, nmt, expert_offsets, (int)E, st);
+  int rc = moe_build_mtiles(mtiles, nmt, expert_offsets, (int)E, R, L.max_mtiles, st);
   if (rc) return rc;
   const void *sg = s_gate, *su = s_up, *sd = s_down;
   int sdt = scale_dtype;
@@ -589,7 +597,7 @@ extern "C" int b200moe_linear_w8(void* out, const void* x, const void* w, const 
   int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
   int rc = moe_fill_identity_offsets(offsets, M, st);
   if (rc) return rc;
-  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, st);
+  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, M, L.max_mtiles, st);
   if (rc) return rc;
   rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.xq), reinterpret_cast<float*>(ws + L.xs), L.ld, x, nullptr,
                           1, M, K, stream);
@@ -681,7 +689,7 @@ extern "C" int b200moe_scaled_mm(void* out, int out_dtype, const void* a, const 
   int32_t* nmt = reinterpret_cast<int32_t*>(ws + L.nmt);
   int rc = moe_fill_identity_offsets(offsets, M, st);
   if (rc) return rc;
-  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, st);
+  rc = moe_build_mtiles(mtiles, nmt, offsets, 1, M, L.max_mtiles, st);
   if (rc) return rc;
   // the kernel applies act_scale[row,kb] * weight_scale[nb,kb] to every 128-deep partial sum: constant grids here
   const int64_t nxs = (K / kBlock) * L.ld, nws = ((N + kBlock - 1) / kBlock) * (K / kBlock);

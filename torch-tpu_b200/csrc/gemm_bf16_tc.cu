@@ -17,6 +17,8 @@
 //               reads (K-major for gemm1, MN-major for gemm2: weights keep the reference layout [E,I,H]), 2 slots
 //   warps 12-15 epilogue: one 256-column accumulator per tile, read once (two tensor-memory buffers: the epilogue of a
 //               tile overlaps the main loop of the next)
+// With bf16 weights (the reference op called with scales = None, python/test/fused_moe_bf16.py:113-122) there is
+// nothing to dequantise: the producer loads the operand tile itself (4 stages of A + B) and warps 4-11 stay idle.
 // No multicast loads.  Every wait is bounded; on a time-out status bit 1 is raised and all roles leave together.
 #include "tc_ptx.cuh"
 
@@ -31,6 +33,9 @@ constexpr int BT_STAGE_BYTES = BT_A_BYTES + BT_RAW_BYTES;
 constexpr int BT_B_BYTES = 256 * BT_BK * 2;   // 32 KB: the dequantised operand tile
 constexpr int BT_BSLOTS = 2;
 constexpr int BT_DEQ_WARPS = 8, BT_EPI_WARPS = 4;
+constexpr int BT_WSTAGE_BYTES = BT_A_BYTES + BT_B_BYTES;  // bf16 weights: a stage is A + the operand tile (48 KB)
+static_assert(BT_STAGES * BT_WSTAGE_BYTES <= BT_STAGES * (BT_A_BYTES + BT_RAW_BYTES) + BT_BSLOTS * BT_B_BYTES,
+              "the bf16-weight ring must fit the space of the two rings it replaces");
 
 struct BtShared {
   uint64_t full[BT_STAGES];    // TMA bytes of the stage have landed
@@ -53,6 +58,8 @@ struct BtArgs {
   const int32_t* offsets;
   const int32_t* row_map;    // gemm2: destination row of sorted row r (NULL = r)
   int H, I, NT, m_major;
+  int P;                     // rows the operand buffers hold: row ranges are clipped to it
+  int bf16w;                 // weights are bf16 [E,I,H] (no scales): B tiles come straight from global memory
   __nv_bfloat16* out;        // gemm1: h [P,I]; gemm2: y rows of H
   int32_t* status;
 };
@@ -147,6 +154,20 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             break;
           }
           const uint32_t full = smem_u32(&sh->full[s]);
+          if (a.bf16w) {  // A + the bf16 operand tile itself: [A 16 KB | B 32 KB] per stage
+            const uint32_t sa = smem_base + s * BT_WSTAGE_BYTES, sb = sa + BT_A_BYTES;
+            mbar_arrive_expect_tx(full, BT_WSTAGE_BYTES);
+            tma_load_2d(sa, &tmA, ks * BT_BK, row0, full);
+            if (!GEMM2) {
+              tma_load_2d(sb, &tmB0, ks * BT_BK, e * a.I + nt * 128, full);                // gate rows, K-major
+              tma_load_2d(sb + 128 * 128, &tmB1, ks * BT_BK, e * a.I + nt * 128, full);    // up rows
+            } else {
+#pragma unroll
+              for (int cn = 0; cn < 4; ++cn)  // four 64-column chunks of (64 K rows x 128 B), MN-major
+                tma_load_2d(sb + cn * (64 * 128), &tmB0, nt * 256 + cn * 64, e * a.I + ks * BT_BK, full);
+            }
+            continue;
+          }
           const uint32_t sa = smem_base + s * BT_STAGE_BYTES, sr = sa + BT_A_BYTES;
           mbar_arrive_expect_tx(full, BT_STAGE_BYTES);
           tma_load_2d(sa, &tmA, ks * BT_BK, row0, full);  // bf16 elements
@@ -166,6 +187,8 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const uint64_t adesc0 = make_smem_desc(smem_base, 16, 1024);
       // gemm1: K-major, 256 rows of 128 B; gemm2: MN-major, four 64-column chunks of (64 K rows x 128 B) = 8 KB each
       const uint64_t bdesc0 = GEMM2 ? make_smem_desc(bslot_base, 64 * 128, 1024) : make_smem_desc(bslot_base, 16, 1024);
+      const uint64_t bdescw0 = GEMM2 ? make_smem_desc(smem_base + BT_A_BYTES, 64 * 128, 1024)
+                                     : make_smem_desc(smem_base + BT_A_BYTES, 16, 1024);
       uint32_t it = 0, n = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++n) {
@@ -175,13 +198,14 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         for (int ks = 0; ks < KS; ++ks, ++it) {
           const uint32_t s = it % BT_STAGES, j = it % BT_BSLOTS;
           if (!mbar_wait(smem_u32(&sh->full[s]), (it / BT_STAGES) & 1, abort_flag) ||
-              !mbar_wait(smem_u32(&sh->bfull[j]), (it / BT_BSLOTS) & 1, abort_flag)) {
+              (!a.bf16w && !mbar_wait(smem_u32(&sh->bfull[j]), (it / BT_BSLOTS) & 1, abort_flag))) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t adesc = adesc0 + (uint64_t)(s * (BT_STAGE_BYTES >> 4));
-          const uint64_t bdesc = bdesc0 + (uint64_t)(j * (BT_B_BYTES >> 4));
+          const uint64_t adesc = adesc0 + (uint64_t)(s * ((a.bf16w ? BT_WSTAGE_BYTES : BT_STAGE_BYTES) >> 4));
+          const uint64_t bdesc = a.bf16w ? bdescw0 + (uint64_t)(s * (BT_WSTAGE_BYTES >> 4))
+                                         : bdesc0 + (uint64_t)(j * (BT_B_BYTES >> 4));
 #pragma unroll
           for (int k16 = 0; k16 < BT_BK / 16; ++k16) {
             // K advances 16 elements: +32 B inside the swizzle atom (K-major) or +16 rows of 128 B (MN-major)
@@ -199,7 +223,7 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int dt = threadIdx.x - 128;  // 0..255
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < total_tiles && ok && !a.bf16w; t += gridDim.x) {
       int nt, mt;
       tile_of(t, nt, mt);
       const int e = a.mtiles[2 * mt];
@@ -275,7 +299,7 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       int nt, mt;
       tile_of(t, nt, mt);
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
-      const int row_end = a.offsets[e + 1];
+      const int row_end = min(a.offsets[e + 1], a.P);
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
       const uint32_t buf = n & 1;
@@ -382,7 +406,11 @@ int launch_bt(const MoeGemmArgs& g, cudaStream_t st) {
   CUtensorMap tmA, tmB0, tmB1;
   // A: bf16 rows, already in sorted order (gemm1: gathered x [P,H]; gemm2: h [P,I])
   if (!bt_make_map(&tmA, g.a16, (uint64_t)g.P, (uint64_t)K, 2, BT_BK, 128, true)) return B200MOE_EDRIVER;
-  if (!GEMM2) {
+  if (g.w_bf16) {  // bf16 weights: operand tiles straight from global memory, 128-byte swizzle
+    const uint32_t br = GEMM2 ? BT_BK : 128;  // gemm1: 128 rows x 64 K elements; gemm2: 64 K rows x 64 columns
+    if (!bt_make_map(&tmB0, g.w0, (uint64_t)g.E * g.I, (uint64_t)g.H, 2, 64, br, true)) return B200MOE_EDRIVER;
+    if (!bt_make_map(&tmB1, GEMM2 ? g.w0 : g.w1, (uint64_t)g.E * g.I, (uint64_t)g.H, 2, 64, br, true)) return B200MOE_EDRIVER;
+  } else if (!GEMM2) {
     if (!bt_make_map(&tmB0, g.w0, (uint64_t)g.E * g.I, (uint64_t)g.H, 1, BT_BK, 128, false)) return B200MOE_EDRIVER;
     if (!bt_make_map(&tmB1, g.w1, (uint64_t)g.E * g.I, (uint64_t)g.H, 1, BT_BK, 128, false)) return B200MOE_EDRIVER;
   } else {
@@ -399,6 +427,8 @@ int launch_bt(const MoeGemmArgs& g, cudaStream_t st) {
   a.row_map = GEMM2 ? g.row_map : nullptr;
   a.H = g.H;
   a.I = g.I;
+  a.P = (int)g.P;
+  a.bf16w = g.w_bf16;
   a.NT = GEMM2 ? (g.H + 255) / 256 : g.I / 128;
   {
     const double a_bytes = (double)g.P * K * 2;

@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(256) gemm1_simple_kernel(MoeGemmArgs a) {
   if (mt >= *a.num_mtiles) return;
   const int e = a.mtiles[2 * mt];
   const int row0 = a.mtiles[2 * mt + 1] + sub * SR;
-  const int row_end = a.offsets[e + 1];
+  const int row_end = min(a.offsets[e + 1], (int)a.P);
   if (row0 >= row_end) return;
   const int tid = threadIdx.x, r = tid >> 4, cg = tid & 15;
   const int H = a.H, I = a.I, nH = H / kBlock, nI = I / kBlock;
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256) gemm2_simple_kernel(MoeGemmArgs a) {
   if (mt >= *a.num_mtiles) return;
   const int e = a.mtiles[2 * mt];
   const int row0 = a.mtiles[2 * mt + 1] + sub * SR;
-  const int row_end = a.offsets[e + 1];
+  const int row_end = min(a.offsets[e + 1], (int)a.P);
   if (row0 >= row_end) return;
   const int tid = threadIdx.x, r = tid >> 4, cg = tid & 15;
   const int H = a.H, I = a.I, nH = H / kBlock, nI = I / kBlock;
@@ -200,13 +200,15 @@ __global__ void __launch_bounds__(256) gemm2_simple_kernel(MoeGemmArgs a) {
 
 __global__ void __launch_bounds__(1024)
 build_mtiles_kernel(int32_t* __restrict__ mtiles, int32_t* __restrict__ num_mtiles,
-                    const int32_t* __restrict__ offsets, int E) {
+                    const int32_t* __restrict__ offsets, int E, int max_rows, int max_mtiles) {
   __shared__ int tmp[1024];
   const int t = threadIdx.x;
   int b = 0, n = 0;
   if (t < E) {
-    b = offsets[t];
-    n = (offsets[t + 1] - b + kTileM - 1) / kTileM;
+    // rows at or past max_rows do not exist in the operand buffers (offsets that a caller computed for more rows
+    // than the buffers hold are clipped here, and every kernel clips its row ranges the same way)
+    b = min(offsets[t], max_rows);
+    n = (min(offsets[t + 1], max_rows) - b + kTileM - 1) / kTileM;
   }
   tmp[t] = n;
   __syncthreads();
@@ -217,11 +219,11 @@ build_mtiles_kernel(int32_t* __restrict__ mtiles, int32_t* __restrict__ num_mtil
     __syncthreads();
   }
   const int base = tmp[t] - n;
-  for (int i = 0; i < n; ++i) {
+  for (int i = 0; i < n && base + i < max_mtiles; ++i) {
     mtiles[2 * (base + i)] = t;
     mtiles[2 * (base + i) + 1] = b + i * kTileM;
   }
-  if (t == 1023) *num_mtiles = tmp[1023];
+  if (t == 1023) *num_mtiles = min(tmp[1023], max_mtiles);
 }
 
 __global__ void identity_offsets_kernel(int32_t* offsets, int T) {
@@ -275,8 +277,9 @@ combine_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict_
 
 }  // namespace
 
-int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, cudaStream_t st) {
-  build_mtiles_kernel<<<1, 1024, 0, st>>>(mtiles, num_mtiles, offsets, E);
+int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, int64_t max_rows,
+                     int max_mtiles, cudaStream_t st) {
+  build_mtiles_kernel<<<1, 1024, 0, st>>>(mtiles, num_mtiles, offsets, E, (int)max_rows, max_mtiles);
   return moe_launch_status();
 }
 

@@ -78,6 +78,7 @@ struct TcArgs {
   const int32_t* row_src;   // down GEMM over peer memory: origin tag (rank << 24 | row) of every row ...
   const uint64_t* out_tbl;  // ... and the per-rank output buffers (device array of pointers)
   int H, I, NT;
+  int P;         // rows the operand buffers hold: row ranges are clipped to it
   int KS;        // K splits (down GEMM of decode-size batches); 1 = none
   int m_major;   // work-item order: 0 = n-tile slow, m-tile fast; 1 = m-tile slow, n-tile fast (see launch_tc)
   float* out32;  // fp32 accumulation target when KS > 1; with KS == 1 (linear layer only): fp32 rows stored instead of bf16
@@ -266,7 +267,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int ks = t % a.KS, tt = t / a.KS;
       const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
       const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
-      const int row_end = a.offsets[e + 1];
+      const int row_end = min(a.offsets[e + 1], a.P);
       const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
       const int KB = kb1 - kb0;  // K blocks of this work item
       const int grow = row0 + rit;
@@ -662,6 +663,7 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   a.out_tbl = g.out_tbl;
   a.H = g.H;
   a.I = g.I;
+  a.P = (int)g.P;
   a.NT = GEMM2 ? (g.H + 255) / 256 : DENSE ? (g.I + 255) / 256 : g.I / 128;
   a.comb32 = (GEMM2 && !g.row_src) ? g.comb32 : nullptr;
   a.comb_w = g.comb_w;

@@ -19,6 +19,7 @@ struct MoeGemmArgs {
   const void* s0;
   const void* s1;
   int scale_dtype;
+  int w_bf16;               // weights are bf16 (no scales): W8A16 tensor-core kernels only
   // tiling
   const int32_t* mtiles;    // int2 {expert, row0} per m-tile
   const int32_t* num_mtiles;
@@ -45,7 +46,9 @@ struct MoeGemmArgs {
   int32_t* status;
 };
 
-int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, cudaStream_t st);
+// tiles of rows [offsets[e], offsets[e+1]) clipped to max_rows; at most max_mtiles entries are written
+int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, int64_t max_rows,
+                     int max_mtiles, cudaStream_t st);
 // identity problem (one expert, rows 0..T): offsets = {0,T}
 int moe_fill_identity_offsets(int32_t* offsets, int64_t T, cudaStream_t st);
 

@@ -14,6 +14,7 @@
 #include <cstring>
 #include <mutex>
 #include <algorithm>
+#include <initializer_list>
 #include <unordered_map>
 #include <utility>
 
@@ -103,6 +104,57 @@ Tensor scales_as_f32(const Tensor& s) {
     it = cache.insert_or_assign(s.data_ptr(), Entry{s.numel(), (uint32_t)s._version(), s.to(kFloat)}).first;
   }
   return it->second.f32;
+}
+
+// bf16-weight experts (scales = None in the reference call, python/test/fused_moe_bf16.py:113-122): same pipeline,
+// the bf16 tensor-core kernels read the weights as they are
+Tensor run_experts_bf16(Tensor& output, const Tensor& input, const Tensor& gate_w, const Tensor& up_w,
+                        const Tensor& down_w, const Tensor& select_experts, const Tensor& routing_weights,
+                        int64_t num_experts, int64_t top_k) {
+  for (const Tensor* t : std::initializer_list<const Tensor*>{&output, &input, &gate_w, &up_w, &down_w, &select_experts,
+                                                              &routing_weights})
+    check_cuda_contig(*t, "fused_moe_fused_experts argument");
+  TORCH_CHECK(select_experts.scalar_type() == kInt, "select_experts must be int32 dtype");
+  TORCH_CHECK(input.dim() == 2 && input.scalar_type() == kBFloat16, "input must be bf16 [T,H]");
+  TORCH_CHECK(output.scalar_type() == kBFloat16, "output must be bf16");
+  TORCH_CHECK(gate_w.scalar_type() == kBFloat16 && up_w.scalar_type() == kBFloat16 && down_w.scalar_type() == kBFloat16,
+              "without block scales the expert weights must be bfloat16");
+  const int64_t T = input.size(0), H = input.size(1);
+  TORCH_CHECK(gate_w.dim() == 3 && gate_w.size(0) == num_experts && gate_w.size(2) == H, "gate_weights must be [E,I,H]");
+  TORCH_CHECK(up_w.sizes() == gate_w.sizes() && down_w.sizes() == gate_w.sizes(),
+              "up/down weights must be [E,I,H] (down = W_down^T, contiguous)");
+  TORCH_CHECK(select_experts.dim() == 2 && select_experts.size(0) == T && select_experts.size(1) == top_k,
+              "select_experts must be [T,k]");
+  TORCH_CHECK(routing_weights.numel() == T * top_k, "routing_weights must be [T,k]");
+  b200moe_experts_desc d{};
+  d.T = T, d.H = H, d.I = gate_w.size(1), d.E = num_experts, d.k = top_k;
+  if (output.dim() == 3) {
+    TORCH_CHECK(output.size(0) == T && output.size(1) == top_k && output.size(2) == H, "output must be [T,k,H]");
+    d.out_mode = B200MOE_OUT_PER_SLOT;
+  } else {
+    TORCH_CHECK(output.dim() == 2 && output.size(0) == T && output.size(1) == H, "output must be [T,k,H] or [T,H]");
+    d.out_mode = B200MOE_OUT_COMBINED;
+  }
+  d.act_mode = B200MOE_ACT_W8A16;
+  d.weights_bf16 = 1;
+  d.scale_dtype = B200MOE_F32;
+  if (routing_weights.scalar_type() == kFloat) d.w_dtype = B200MOE_F32;
+  else if (routing_weights.scalar_type() == kBFloat16) d.w_dtype = B200MOE_BF16;
+  else TORCH_CHECK(false, "routing_weights must be float32 or bfloat16");
+  c10::cuda::CUDAGuard guard(input.device());
+  cudaStream_t st = at::cuda::getCurrentCUDAStream();
+  const size_t need = b200moe_experts_workspace_bytes(&d);
+  TORCH_CHECK(need > 0 || T == 0, "fused_moe_fused_experts: unsupported sizes (H and I must be multiples of 128)");
+  Tensor ws = workspace_for(input.device(), st, need);
+  void* wsp = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws.data_ptr()) + 255) & ~uintptr_t(255));
+  const size_t ws_bytes = (size_t)ws.numel() - (reinterpret_cast<char*>(wsp) - reinterpret_cast<char*>(ws.data_ptr()));
+  Tensor status = status_word(input.device());
+  check_rc(b200moe_experts(output.data_ptr(), input.data_ptr(), gate_w.data_ptr(), up_w.data_ptr(), down_w.data_ptr(),
+                           nullptr, nullptr, nullptr, select_experts.data_ptr<int32_t>(), routing_weights.data_ptr(),
+                           nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, &d, wsp, ws_bytes,
+                           status.data_ptr<int32_t>(), st),
+           "b200moe_experts");
+  return output;
 }
 
 Tensor run_experts(Tensor& output, const Tensor& input, const Tensor& gate_w, const Tensor& up_w,
@@ -215,13 +267,16 @@ Tensor fused_moe_fused_experts(
     const c10::optional<Tensor>& silu, const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0,
     bool save_mid_res) {
   reject_unused(output_sample, input_sample, num_select_experts, silu, sigmoid, m0, save_mid_res);
-  TORCH_CHECK(gate_scales.has_value() && up_scales.has_value() && down_scales.has_value(),
-              "fused_moe_fused_experts: FP8 weights need their block scales (bf16-weight experts are out of scope)");
   (void)select_experts_middle;  // caller scratch of the reference kernels; not needed here
   (void)routing_weights_middle;
   (void)use_grouped_topk;       // routing is already done: select_experts is an input
   (void)num_expert_group;
   (void)topk_group;
+  if (!gate_scales.has_value() && !up_scales.has_value() && !down_scales.has_value())
+    return run_experts_bf16(output, input, gate_weights, up_weights, down_weights, select_experts, routing_weights,
+                            num_experts, num_experts_per_tok);
+  TORCH_CHECK(gate_scales.has_value() && up_scales.has_value() && down_scales.has_value(),
+              "fused_moe_fused_experts: FP8 weights need all three block-scale tensors");
   return run_experts(output, input, gate_weights, up_weights, down_weights, gate_scales.value(), up_scales.value(),
                      down_scales.value(), select_experts, routing_weights, blocksize, num_experts,
                      num_experts_per_tok, act_mode_from_env());

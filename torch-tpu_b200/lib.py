@@ -25,7 +25,7 @@ class ExpertsDesc(Structure):
     _fields_ = [("T", c_int64), ("H", c_int64), ("I", c_int64), ("E", c_int64), ("k", c_int64),
                 ("I_shared", c_int64), ("out_mode", c_int), ("act_mode", c_int), ("impl", c_int),
                 ("scale_dtype", c_int), ("w_dtype", c_int), ("impl_gate_up", c_int), ("impl_down", c_int),
-                ("stages", c_int)]
+                ("weights_bf16", c_int), ("stages", c_int)]
 
 
 # name -> (restype, argtypes): every symbol include/b200moe.h declares

@@ -116,9 +116,9 @@ def quant_rows(x, row_map=None, div=1):
 
 def make_desc(T, H, I, E, k, *, I_shared=0, out_mode=L.OUT_PER_SLOT, act_mode=L.ACT_W8A8, impl=L.IMPL_AUTO,
               scale_dtype=torch.float32, w_dtype=torch.float32, impl_gate_up=L.IMPL_AUTO, impl_down=L.IMPL_AUTO,
-              stages=0):
+              weights_bf16=False, stages=0):
     return L.ExpertsDesc(T, H, I, E, k, I_shared, out_mode, act_mode, impl, _DT[scale_dtype], _DT[w_dtype],
-                         impl_gate_up, impl_down, stages)
+                         impl_gate_up, impl_down, int(weights_bf16), stages)
 
 
 def experts_workspace_bytes(desc):
@@ -135,10 +135,14 @@ def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, ac
     mask of ``L.STAGE_*`` to re-run part of a call on a workspace that a whole call has filled.  Returns ``out``."""
     _chk(out, "out", torch.bfloat16)
     _chk(x, "x", torch.bfloat16)
+    bf16w = wg.dtype == torch.bfloat16      # bf16 weights carry no scales: sg/su/sd may be None
     for n, t in (("wg", wg), ("wu", wu), ("wd", wd)):
-        _chk(t, n, torch.float8_e4m3fn)
-    for n, t in (("sg", sg), ("su", su), ("sd", sd)):
-        _chk(t, n, sg.dtype)
+        _chk(t, n, torch.bfloat16 if bf16w else torch.float8_e4m3fn)
+    if bf16w:
+        act_mode = L.ACT_W8A16
+    else:
+        for n, t in (("sg", sg), ("su", su), ("sd", sd)):
+            _chk(t, n, sg.dtype)
     _chk(ids, "ids", torch.int32)
     T, H = x.shape
     E, I, _ = wg.shape
@@ -146,8 +150,9 @@ def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, ac
     out_mode = L.OUT_PER_SLOT if out.dim() == 3 else (L.OUT_COMBINED_FUSED if fused_combine else L.OUT_COMBINED)
     I_shared = shared[0].shape[-2] if shared is not None else 0
     d = make_desc(T, H, I, E, k, I_shared=I_shared, out_mode=out_mode, act_mode=act_mode, impl=impl,
-                  scale_dtype=sg.dtype, w_dtype=topk_w.dtype if topk_w is not None else torch.float32,
-                  impl_gate_up=impl_gate_up, impl_down=impl_down, stages=stages)
+                  scale_dtype=torch.float32 if bf16w else sg.dtype,
+                  w_dtype=topk_w.dtype if topk_w is not None else torch.float32,
+                  impl_gate_up=impl_gate_up, impl_down=impl_down, weights_bf16=bf16w, stages=stages)
     need = experts_workspace_bytes(d)
     if need == 0 and T > 0:
         raise ValueError("unsupported sizes for b200moe_experts (H, I multiples of 128; see include/b200moe.h)")
