@@ -93,12 +93,8 @@ struct TcArgs {
   int32_t* status;
 };
 
-// A pair of fp32 accumulators.  Two forms: one fma.rn.f32x2 per pair (half the instruction slots) or two scalar
-// FMAs (MOE_TC_SCALAR_FMA; the form the TMEM-read microbenchmark found a little faster on this part).
-#ifndef MOE_TC_SCALAR_FMA
-#define MOE_TC_SCALAR_FMA 1
-#endif
-#if MOE_TC_SCALAR_FMA
+// A pair of fp32 accumulators (two scalar FMAs per pair: on this part the packed fma.rn.f32x2 form was no faster in
+// the tensor-memory read-back loop, and the scalar form leaves the register allocator free to place the pairs)
 struct acc2_t {
   float x, y;
 };
@@ -107,30 +103,7 @@ __device__ __forceinline__ acc2_t pack2(float lo, float hi) { return acc2_t{lo, 
 __device__ __forceinline__ acc2_t pack2u(uint32_t lo, uint32_t hi) { return acc2_t{__uint_as_float(lo), __uint_as_float(hi)}; }
 __device__ __forceinline__ float2 unpack2(acc2_t v) { return make_float2(v.x, v.y); }
 __device__ __forceinline__ acc2_t ffma2(acc2_t a, acc2_t b, acc2_t c) { return acc2_t{fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y)}; }
-#else
-typedef uint64_t acc2_t;
-__device__ __forceinline__ acc2_t acc2_zero() { return 0ull; }
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  return r;
-}
-__device__ __forceinline__ float2 unpack2(uint64_t v) {
-  float2 r;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
-  return r;
-}
-__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t d;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-  return d;
-}
-#endif
+
 // SiLU through one special-function operation per value: x * sigmoid(x) with sigmoid(x) = 0.5 * tanh(0.5 x) + 0.5
 // (tanh.approx.f32, absolute error of the sigmoid below 2^-11: far inside the e4m3 requantisation that follows; the
 // exp + reciprocal form costs two such operations, and the tile end of the gate/up GEMM is bound by that unit)
@@ -329,40 +302,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i] =
                 ffma2(pack2u(sv[2 * i], sv[2 * i + 1]), fp, acc[c / TC_CPH][(c % TC_CPH) * (TC_CH / 2) + i]);
         };
-#if MOE_TC_PIPE == 0
-        for (int kb = 0; kb < KB && ok; ++kb, ++it) {   // strict order, block by block
-          f0p = pack2(f0, f0), f1p = pack2(f1, f1);
-          const float nf0 = sa1 * wa1, nf1 = sa1 * wb1;
-          if (kb + 2 < KB) {
-            sa1 = load_sa(kb + 2);
-            wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
-            wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
-          }
-          if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t tb = lane_base + (it & 1) * 256;
-          tc_ld_issue(chunk_addr(tb, 0), s0);
-          tc_ld_issue(chunk_addr(tb, 1), s1);
-          tc_ld_wait(s0, s1);
-#pragma unroll
-          for (int c = 0; c < TC_NC - 2; c += 2) {
-            fma_chunk(c, s0);
-            tc_ld_issue(chunk_addr(tb, c + 2), s0);
-            fma_chunk(c + 1, s1);
-            tc_ld_issue(chunk_addr(tb, c + 3), s1);
-            tc_ld_wait(s0, s1);
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[it & 1]));
-          fma_chunk(TC_NC - 2, s0);
-          fma_chunk(TC_NC - 1, s1);
-          f0 = nf0, f1 = nf1;
-        }
-#else
         if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) ok = false;
         if (ok) {
           tc_fence_after();
@@ -375,7 +314,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           const uint32_t tb = lane_base + (it & 1) * 256;
           f0p = pack2(f0, f0), f1p = pack2(f1, f1);
           const float nf0 = sa1 * wa1, nf1 = sa1 * wb1;  // block kb + 1
-          if (kb + 2 < KB && !(MOE_TC_ABL & 1)) {
+          if (kb + 2 < KB) {
             sa1 = load_sa(kb + 2);
             wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
             wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
@@ -390,21 +329,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (c + 4 < TC_NC) tc_ld_wait(s0, s1);
           }
           const uint32_t nbar = smem_u32(&sh->empty[(it + 1) % TC_STAGES]), npar = ((it + 1) / TC_STAGES) & 1;
-#if MOE_TC_PIPE == 1
-          // the last two chunks of this block are in flight: wait for the next block's accumulator meanwhile
-          bool next_ready = more ? mbar_wait(nbar, npar, abort_flag) : false;
-          if (more && !next_ready) ok = false;
-#else
           // The last two chunks of this block are in flight.  Is the next block's accumulator there already (it is
           // whenever this warp is what the MMAs wait for)?  Only a test: the buffer goes back before any real wait,
           // or the MMA issuer, which needs this buffer for block kb + 2, would idle until block kb + 1 is done.
           const bool next_ready = more && mbar_test(nbar, npar);
-#endif
           tc_ld_wait(s0, s1);
           tc_fence_before();  // all of this block is in registers: hand the buffer back
           __syncwarp();
           if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[it & 1]));
-          if (!ok) break;
           const uint32_t tn = lane_base + ((it + 1) & 1) * 256;
           if (next_ready) {
             tc_fence_after();
@@ -418,7 +350,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             if (more) {
               if (!mbar_wait(nbar, npar, abort_flag)) {
                 ok = false;
-                ++it;
                 break;
               }
               tc_fence_after();
@@ -428,7 +359,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           f0 = nf0, f1 = nf1;
         }
-#endif
       }
       float amax = 0.f;
       if (MODE == 0) {

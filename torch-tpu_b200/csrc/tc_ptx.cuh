@@ -23,12 +23,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-#ifndef MOE_TC_ABL
-#define MOE_TC_ABL 0
-#endif
-#ifndef MOE_TC_PIPE
-#define MOE_TC_PIPE 2
-#endif
 #ifndef MOE_TC_HINT
 #define MOE_TC_HINT 2000
 #endif
