@@ -10,16 +10,26 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 constexpr int64_t kSplitMaxPairs = 512;  // the down GEMM splits K over CTAs only for batches this small
 
-// K splits of the down GEMM: with few (token,slot) pairs there are fewer output tiles than SMs and every tile has a
-// long K loop (K = I), so the weight stream would be pulled by a handful of SMs.
+// K splits of the down GEMM.  With few (token,slot) pairs there are fewer output tiles than SMs and every tile has a
+// long K loop (K = I), so the weight stream would be pulled by a handful of SMs, or by one and a half waves of work
+// items.  The critical path of a persistent launch is (waves of work items) x (K blocks per item), plus what the
+// partial sums cost: every split adds one fp32 reduction per output value, and reductions that meet at one address
+// are slow (measured: at 1024 pairs a 3-way split lost more than it won, so larger batches are never split - which
+// also keeps every prefill-size result bit-reproducible).  Pick the split that makes the sum shortest.  The number
+// of m-tiles is a device-side value; the host estimates it from the sizes.
 int choose_ksplit(int64_t P, int64_t E, int64_t H, int64_t I) {
   if (P > kSplitMaxPairs) return 1;
-  const int64_t tiles = (P < E ? P : E) * ((H + 255) / 256);
-  int64_t ks = (moe_device_sm_count() + tiles - 1) / tiles;
-  const int64_t kb = I / kBlock;
-  if (ks > kb / 4) ks = kb / 4;
-  if (ks > 8) ks = 8;
-  return ks < 1 ? 1 : (int)ks;
+  const int64_t experts = P < E ? P : E;                    // activated experts, at most
+  const int64_t mtiles_even = (3 * P / 2 + kTileM - 1) / kTileM;  // uneven loads: some experts spill into a second tile
+  const int64_t tiles = (experts > mtiles_even ? experts : mtiles_even) * ((H + 255) / 256);
+  const int64_t kb = I / kBlock, sms = moe_device_sm_count();
+  int best = 1;
+  int64_t best_cost = ((tiles + sms - 1) / sms) * kb;
+  for (int ks = 2; ks <= 16 && ks * 2 <= kb; ++ks) {
+    const int64_t cost = ((tiles * ks + sms - 1) / sms) * ((kb + ks - 1) / ks) + P * (H / 4) * ks / 30000;
+    if (cost * 100 < best_cost * 97) best = ks, best_cost = cost;  // a split must buy at least 3 %
+  }
+  return best;
 }
 
 struct WsLayout {
@@ -58,7 +68,10 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   // combined output: per-slot rows for the separate combine kernel; the fused combine adds into an fp32 [T,H] buffer
   // instead (both are laid out, so that one workspace serves either mode of the same sizes)
   L.y = take(d.out_mode != B200MOE_OUT_PER_SLOT ? (size_t)P * d.H * 2 : 0);
-  L.acc32 = take(d.out_mode == B200MOE_OUT_COMBINED_FUSED && w8a8 ? (size_t)d.T * d.H * sizeof(float) : 0);
+  // (also used by B200MOE_OUT_COMBINED at decode sizes: the K-split partial sums of the down GEMM are reductions
+  // anyway, so they go straight into the combined rows instead of through per-slot rows and the combine kernel)
+  L.acc32 = take((d.out_mode == B200MOE_OUT_COMBINED_FUSED || (d.out_mode == B200MOE_OUT_COMBINED && P <= kSplitMaxPairs)) && w8a8
+                     ? (size_t)d.T * d.H * sizeof(float) : 0);
   // fp32 partial sums of the K-split down GEMM (decode-size batches only)
   // (sized for min(P, limit) rows whatever P is, so that the workspace size never shrinks when T grows)
   L.y32 = take(w8a8 ? (size_t)(P < kSplitMaxPairs ? P : kSplitMaxPairs) * d.H * sizeof(float) : 0);
@@ -183,7 +196,8 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   const bool tc1_16 = !w8a8 && moe_tc_available() && (d->impl_gate_up ? d->impl_gate_up == B200MOE_IMPL_TCGEN05 : use_tc16);
   const bool tc2_16 = !w8a8 && moe_tc_available() && (d->impl_down ? d->impl_down == B200MOE_IMPL_TCGEN05 : use_tc16);
   // the fused combine lives in the tensor-core down GEMM's epilogue; other paths combine with the separate kernel
-  const bool fused = d->out_mode == B200MOE_OUT_COMBINED_FUSED && tc2;
+  const int ksplit = tc2 ? choose_ksplit(L.P, d->E, d->H, d->I) : 1;
+  const bool fused = tc2 && (d->out_mode == B200MOE_OUT_COMBINED_FUSED || (d->out_mode == B200MOE_OUT_COMBINED && ksplit > 1));
   // a stage may be re-run alone on a workspace that a whole call of the same sizes has filled
   const int stages = d->stages ? d->stages : B200MOE_STAGE_ALL;
   const bool do_prep = stages & B200MOE_STAGE_PREP, do_g1 = stages & B200MOE_STAGE_GATE_UP,
@@ -205,10 +219,14 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   }
 
   if (do_prep) {
-    rc = b200moe_permute(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, stream);
+    bool tiles_done = false;
+    rc = moe_permute_impl(I32(L.sorted), I32(L.offsets), ids, d->T, d->k, d->E, I32(L.scratch), status, I32(L.mtiles),
+                          I32(L.nmt), L.max_mtiles, &tiles_done, stream);
     if (rc) return rc;
-    rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, L.P, L.max_mtiles, st);
-    if (rc) return rc;
+    if (!tiles_done) {
+      rc = moe_build_mtiles(I32(L.mtiles), I32(L.nmt), I32(L.offsets), (int)d->E, L.P, L.max_mtiles, st);
+      if (rc) return rc;
+    }
   }
   if (w8a8 && do_prep) {
     rc = b200moe_quant_rows(reinterpret_cast<uint8_t*>(ws + L.xq), reinterpret_cast<float*>(ws + L.xs), L.ld,
@@ -285,7 +303,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     if (tc2) {
       MoeGemmArgs t = g2;
       if (cvt) t.s0 = sc32 + 2 * nsc, t.scale_dtype = B200MOE_F32;
-      t.ksplit = choose_ksplit(L.P, d->E, d->H, d->I);
+      t.ksplit = ksplit;
       if (fused) {
         t.comb32 = acc32;
         t.comb_w = topk_w;

@@ -46,6 +46,10 @@ struct MoeGemmArgs {
   int32_t* status;
 };
 
+// b200moe_permute that also writes the m-tile list when one CTA does the whole sort (at most 1024 pairs)
+int moe_permute_impl(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T, int64_t k, int64_t E,
+                     int32_t* scratch, int32_t* status, int32_t* mtiles, int32_t* num_mtiles, int max_mtiles,
+                     bool* tiles_done, void* stream);
 // tiles of rows [offsets[e], offsets[e+1]) clipped to max_rows; at most max_mtiles entries are written
 int moe_build_mtiles(int32_t* mtiles, int32_t* num_mtiles, const int32_t* offsets, int E, int64_t max_rows,
                      int max_mtiles, cudaStream_t st);

@@ -14,6 +14,7 @@ namespace {
 
 constexpr int kChunk = 1024;  // pairs per CTA (32 warps)
 constexpr int kMaxE = 1024;
+constexpr int kRowsPerTile = 128;  // rows of one m-tile of the grouped GEMMs
 constexpr int kMaxDevices = 64;  // per-device caches below are indexed by the CUDA device ordinal
 
 // Per-warp histogram of this chunk in shared memory: wh[w*E + e].  Returns the pair's expert (or -1)
@@ -111,7 +112,8 @@ permute_scatter_kernel(const int32_t* __restrict__ ids, int64_t P, int E,
 // P <= 1024: histogram, scan and scatter in one CTA
 __global__ void __launch_bounds__(kChunk)
 permute_small_kernel(const int32_t* __restrict__ ids, int64_t P, int E, int32_t* __restrict__ offsets,
-                     int32_t* __restrict__ sorted_pair, int32_t* status) {
+                     int32_t* __restrict__ sorted_pair, int32_t* status, int32_t* __restrict__ mtiles,
+                     int32_t* __restrict__ num_mtiles, int max_mtiles) {
   extern __shared__ int wh[];
   __shared__ int tmp[kChunk];
   __shared__ int soffs[kMaxE + 1];
@@ -131,6 +133,22 @@ permute_small_kernel(const int32_t* __restrict__ ids, int64_t P, int E, int32_t*
   for (int i = threadIdx.x; i <= E; i += blockDim.x) offsets[i] = soffs[i];
   if (e >= 0) sorted_pair[soffs[e] + wh[(threadIdx.x >> 5) * E + e] + rank] = (int32_t)threadIdx.x;
   if ((int64_t)threadIdx.x < P && (int)threadIdx.x >= soffs[E]) sorted_pair[threadIdx.x] = -1;  // dropped pairs: see above
+  if (mtiles) {
+    // the m-tile list of the grouped GEMMs ({expert, first row} per 128 rows of an expert) from the same offsets:
+    // one launch less on the decode path
+    __syncthreads();
+    const int t = threadIdx.x;
+    const int b = t < E ? soffs[t] : 0;
+    const int n = t < E ? (soffs[t + 1] - b + kRowsPerTile - 1) / kRowsPerTile : 0;
+    __shared__ int toffs[kMaxE + 1];
+    block_exclusive_scan(n, E, toffs, tmp);
+    __syncthreads();
+    for (int i = 0; i < n && toffs[t] + i < max_mtiles; ++i) {
+      mtiles[2 * (toffs[t] + i)] = t;
+      mtiles[2 * (toffs[t] + i) + 1] = b + i * kRowsPerTile;
+    }
+    if (t == 0) *num_mtiles = min(toffs[E], max_mtiles);
+  }
 }
 
 __global__ void gather_scatter_index_kernel(int32_t* __restrict__ gather_index,
@@ -201,8 +219,12 @@ extern "C" size_t b200moe_permute_scratch_ints(int64_t P, int64_t E) {
   return (size_t)((P + kChunk - 1) / kChunk) * (size_t)E;
 }
 
-extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
-                               int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream) {
+// b200moe_permute; with `mtiles` != NULL and at most 1024 pairs the one-CTA kernel writes the GEMMs' m-tile list too and
+// *tiles_done is set (else the caller builds the list from expert_offsets)
+int moe_permute_impl(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T, int64_t k, int64_t E,
+                     int32_t* scratch, int32_t* status, int32_t* mtiles, int32_t* num_mtiles, int max_mtiles,
+                     bool* tiles_done, void* stream) {
+  if (tiles_done) *tiles_done = false;
   MOE_CHECK_ARG(sorted_pair && expert_offsets && ids && T >= 0 && k > 0 && E > 0);
   const int64_t P = T * k;
   MOE_CHECK_SHAPE(E <= kMaxE && P < (1 << 24));
@@ -219,7 +241,9 @@ extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, co
     attr_done[dev] = true;
   }
   if (P <= kChunk) {
-    permute_small_kernel<<<1, kChunk, smem, st>>>(ids, P, (int)E, expert_offsets, sorted_pair, status);
+    permute_small_kernel<<<1, kChunk, smem, st>>>(ids, P, (int)E, expert_offsets, sorted_pair, status, mtiles,
+                                                  num_mtiles, max_mtiles);
+    if (tiles_done) *tiles_done = mtiles != nullptr;
     return moe_launch_status();
   }
   MOE_CHECK_ARG(scratch);
@@ -228,6 +252,12 @@ extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, co
   permute_scan_kernel<<<1, kChunk, 0, st>>>(scratch, nchunks, (int)E, expert_offsets);
   permute_scatter_kernel<<<nchunks, kChunk, smem, st>>>(ids, P, (int)E, scratch, expert_offsets, sorted_pair);
   return moe_launch_status();
+}
+
+extern "C" int b200moe_permute(int32_t* sorted_pair, int32_t* expert_offsets, const int32_t* ids, int64_t T,
+                               int64_t k, int64_t E, int32_t* scratch, int32_t* status, void* stream) {
+  return moe_permute_impl(sorted_pair, expert_offsets, ids, T, k, E, scratch, status, nullptr, nullptr, 0, nullptr,
+                          stream);
 }
 
 extern "C" int b200moe_gather_scatter_index(int32_t* gather_index, int32_t* scatter_index,
