@@ -244,7 +244,8 @@ def launches_per_step(wl, T, world=1, ep="nccl"):
         if wl.get("shared"):
             n += (1 if T <= 1024 else 3) + 1 + 1 + 2      # permute (identity ids), tiles, quant, 2 GEMMs
         return n
-    n = 2 + (1 if P <= 1024 else 3) + 1 + 1 + 2 + 1   # router, route, permute, tiles, quant, 2 GEMMs, combine
+    # router, route, permute (+ tiles: one kernel up to 1024 pairs, else 3 + 1), quant, 2 GEMMs, combine
+    n = 2 + (1 if P <= 1024 else 4) + 1 + 2 + 1
     if wl.get("shared"):
         n += 2 + 1 + 2                                  # identity offsets + tiles, quant, 2 GEMMs
     return n

@@ -70,8 +70,11 @@ WsLayout make_layout(const b200moe_experts_desc& d) {
   L.y = take(d.out_mode != B200MOE_OUT_PER_SLOT ? (size_t)P * d.H * 2 : 0);
   // (also used by B200MOE_OUT_COMBINED at decode sizes: the K-split partial sums of the down GEMM are reductions
   // anyway, so they go straight into the combined rows instead of through per-slot rows and the combine kernel)
-  L.acc32 = take((d.out_mode == B200MOE_OUT_COMBINED_FUSED || (d.out_mode == B200MOE_OUT_COMBINED && P <= kSplitMaxPairs)) && w8a8
-                     ? (size_t)d.T * d.H * sizeof(float) : 0);
+  // (in that case for min(T, limit) tokens whatever T is, so that the workspace size never shrinks when T grows)
+  const int64_t acc_tokens = d.out_mode == B200MOE_OUT_COMBINED_FUSED ? d.T
+                             : d.out_mode == B200MOE_OUT_COMBINED     ? (d.T < kSplitMaxPairs ? d.T : kSplitMaxPairs)
+                                                                      : 0;
+  L.acc32 = take(w8a8 ? (size_t)acc_tokens * d.H * sizeof(float) : 0);
   // fp32 partial sums of the K-split down GEMM (decode-size batches only)
   // (sized for min(P, limit) rows whatever P is, so that the workspace size never shrinks when T grows)
   L.y32 = take(w8a8 ? (size_t)(P < kSplitMaxPairs ? P : kSplitMaxPairs) * d.H * sizeof(float) : 0);

@@ -7,13 +7,14 @@
 //          (stands in for the gate/up part of my_ops/fusedMoE.pl:217-259)
 //   gemm2  y = h Wd                      per expert, rows scattered to their (token,slot) position
 //          (my_ops/fusedMoE.pl:264-269 + scatter_store :55-96); with a peer table the rows go straight to
-//          the rank that owns the token (expert parallelism over peer memory: plain peer stores, a warp
-//          stores 256 contiguous bytes of one row after the half tile was turned through shared memory)
+//          the rank that owns the token (expert parallelism over peer memory: plain peer stores)
 //   linear out = x W^T with W [N,K]      one "expert", no activation, bf16 rows out (my_ops/MmW8A16Dq.cpp:185-229)
 //
 // One persistent CTA per SM, 12 warps: warp 0 = TMA producer, warp 1 = MMA issuer (one thread) and TMEM
-// owner, warps 2-3 idle (they only give their registers away), warps 4..11 = epilogue (TMEM lane quarter =
-// warp%4, column half = (warp-4)/4).  setmaxnreg moves registers from the first warpgroup to the epilogue.
+// owner, warp 2 = scout (walks the next work item's expert, row range and first scales and leaves them in shared
+// memory), warp 3 idle, warps 4..11 = epilogue (TMEM lane quarter = warp%4, column half = (warp-4)/4).  setmaxnreg
+// moves registers from the first warpgroup to the epilogue.  Results leave through shared memory: every epilogue warp
+// turns its 32 rows x 64 columns through a private patch and stores whole 64- or 128-byte row segments.
 // A tile is 128 rows x 256 MMA columns: gemm1 -> 128 gate + 128 up columns of one 128-wide slice of I
 // (so SiLU*up and the 1x128 requantisation stay inside the CTA); gemm2 -> 256 columns of H.
 // Weights keep the reference layout [E,I,H]: for gemm1 the B operand is K-major, for gemm2 (K = I is the
@@ -34,7 +35,7 @@ constexpr int TC_CH = 16;                    // columns per tcgen05.ld (= regist
 constexpr int TC_CPH = TC_CW / TC_CH;        // TMEM chunks per half
 constexpr int TC_NC = 2 * TC_CPH;            // chunks per thread and K block
 constexpr int TC_EPI_THREADS = 128 * TC_CG;
-constexpr int TC_THREADS = 128 + TC_EPI_THREADS;  // warpgroup 0 = {producer, MMA, 2 idle}, then the epilogue warps
+constexpr int TC_THREADS = 128 + TC_EPI_THREADS;  // warpgroup 0 = {producer, MMA, scout, idle}, then the epilogue warps
 // setmaxnreg targets: warpgroup 0 gives registers to the epilogue.  The increase blocks until the CTA's pool (the
 // launch-time count x threads) holds enough, so 128 * LO + TC_EPI_THREADS * HI must not exceed that pool:
 // 384 threads x 168 = 128 x 72 + 256 x 216; 640 threads x 96 = 128 x 32 + 512 x 112.
@@ -57,10 +58,15 @@ struct TcShared {
   uint64_t empty[TC_STAGES];  // MMAs of the stage's K block are complete: the stage may be refilled AND the block's
                               // accumulator buffer may be read (one tcgen05.commit per K block serves both)
   uint64_t tmem_empty[2];
+  uint64_t head_full, head_empty;  // one-slot hand-over of a work item's starting values (scout warp -> epilogue warps)
   uint32_t tmem_base;
   int abort_flag;
-  // down GEMM with peer output: one 128 x 128 bf16 half tile on its way to row-wise stores;
-  // gate/up GEMM: the row maxima the epilogue's column groups exchange, float [2][TC_CG][128]
+  int head_rows[4];        // expert, first row, end of the expert's rows
+  float head_w[4];         // weight scales of the item's first two K blocks: (gate|half 0, up|half 1) x 2
+  float head_sa[2][128];   // activation scales of the first two K blocks, per row of the tile
+  // results on their way to row-segment stores, one private patch per epilogue warp (down GEMM: 32 rows x 128 B at
+  // warp * 4096; gate/up GEMM: 32 rows x 64 B at 4096 + warp * 2048, behind the row maxima that the epilogue's column
+  // groups exchange, float [2][TC_CG][128])
   alignas(16) uint8_t ostage[128 * 256];
 };
 constexpr size_t TC_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)TC_STAGES * TC_STAGE_BYTES + sizeof(TcShared);
@@ -141,6 +147,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&sh->tmem_empty[b]), 4 * TC_CG);
     }
+    mbar_init(smem_u32(&sh->head_full), 1);
+    mbar_init(smem_u32(&sh->head_empty), 4 * TC_CG);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -160,16 +168,52 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int KB_all = (GEMM2 ? a.I : a.H) / kBlock;
   const int nH = a.H / kBlock, nI = a.I / kBlock;
 
+  // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here.
+  // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
+  // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
+  const float* const S0 = reinterpret_cast<const float*>(a.s0);
+  const float* const S1 = (GEMM2 || DENSE) ? S0 : reinterpret_cast<const float*>(a.s1);  // one scale tensor
+  const int sstep = GEMM2 ? nH : 1;
+  const int nIs = (a.I + kBlock - 1) / kBlock;  // scale rows of one expert (= nI unless a linear layer's N % 128 != 0)
+  struct Item {
+    int nt, mt, kb0, KB;
+  };
+  auto item_of = [&](int t) {
+    Item w;
+    const int ks = t % a.KS, tt = t / a.KS;
+    w.nt = a.m_major ? tt % a.NT : tt / num_mtiles;
+    w.mt = a.m_major ? tt / a.NT : tt - w.nt * num_mtiles;
+    w.kb0 = (int)((int64_t)KB_all * ks / a.KS);
+    w.KB = (int)((int64_t)KB_all * (ks + 1) / a.KS) - w.kb0;  // K blocks of this work item
+    return w;
+  };
+  // (32-bit: the launcher refuses scale tensors of 2^31 elements or more)
+  auto scale_index = [&](const Item& w, int e, int& w0i, int& w1i) {
+    w0i = (GEMM2 ? e * nI * nH + 2 * w.nt : DENSE ? (e * nIs + 2 * w.nt) * nH : (e * nI + w.nt) * nH) + w.kb0 * sstep;
+    w1i = w0i + (GEMM2 ? ((2 * w.nt + 1 < nH) ? 1 : 0) : DENSE ? ((2 * w.nt + 1 < nIs) ? nH : 0) : 0);
+  };
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REG_LO));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      // the m-tile list entry of the NEXT work item is requested while this one's loads are issued: when the weights
+      // stream from HBM the ring is empty at every tile start, and a dependent L2 round trip there is pure idle time
+      auto mtile_of = [&](int t) {
+        const int tt = t / a.KS;
+        return a.m_major ? tt / a.NT : tt % num_mtiles;
+      };
+      int nx_e = 0, nx_row0 = 0;
+      if ((int)blockIdx.x < total_tiles) nx_e = a.mtiles[2 * mtile_of(blockIdx.x)], nx_row0 = a.mtiles[2 * mtile_of(blockIdx.x) + 1];
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const int ks = t % a.KS, tt = t / a.KS;
-        const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
-        const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
+        const int nt = a.m_major ? tt % a.NT : tt / num_mtiles;
+        const int e = nx_e, row0 = nx_row0;
+        if (t + (int)gridDim.x < total_tiles) {
+          const int mn = mtile_of(t + gridDim.x);
+          nx_e = a.mtiles[2 * mn], nx_row0 = a.mtiles[2 * mn + 1];
+        }
         const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % TC_STAGES;
@@ -228,6 +272,41 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         tc_commit(smem_u32(&sh->empty[s]));  // wakes the producer (refill) and the epilogue (accumulator ready)
       }
     }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ scout: the next work item's starting values
+    // What an item starts from sits behind three dependent L2 round trips (m-tile list -> the expert's row range ->
+    // the scales of the first two K blocks): 2000 to 3000 cycles when an epilogue warp walks them at the start of the
+    // item, a tenth of a short item, and the epilogue's K loop has no registers to carry them ahead.  This warp walks
+    // them one item ahead and leaves them in shared memory.
+    bool ok = true;
+    uint32_t n = 0;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++n) {
+      const Item w = item_of(t);
+      const int e = a.mtiles[2 * w.mt], row0 = a.mtiles[2 * w.mt + 1];
+      const int row_end = min(a.offsets[e + 1], a.P);
+      int w0i, w1i;
+      scale_index(w, e, w0i, w1i);
+      float sa[2][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = row0 + i * 32 + lane;
+        sa[0][i] = row < row_end ? a.as_t[(int64_t)w.kb0 * a.ld + row] : 0.f;
+        sa[1][i] = row < row_end && w.KB > 1 ? a.as_t[(int64_t)(w.kb0 + 1) * a.ld + row] : 0.f;
+      }
+      float wv = 0.f;  // lanes 0..3: S0[w0i], S1[w1i], S0[w0i + sstep], S1[w1i + sstep]
+      if (lane < 2 || (lane < 4 && w.KB > 1)) wv = ((lane & 1) ? S1 : S0)[((lane & 1) ? w1i : w0i) + ((lane >> 1) ? sstep : 0)];
+      // the slot is free once every epilogue warp has taken item n - 1 out of it
+      if (n > 0 && !mbar_wait(smem_u32(&sh->head_empty), (n - 1) & 1, abort_flag)) {
+        ok = false;
+        break;
+      }
+      if (lane == 0) sh->head_rows[0] = e, sh->head_rows[1] = row0, sh->head_rows[2] = row_end;
+      if (lane < 4) sh->head_w[lane] = wv;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sh->head_sa[0][i * 32 + lane] = sa[0][i], sh->head_sa[1][i * 32 + lane] = sa[1][i];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->head_full));
+    }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue (4 * TC_CG warps)
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TC_REG_HI));
@@ -237,42 +316,34 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     bool ok = true;
     int ntile = 0;  // work items this CTA has finished
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++ntile) {
-      const int ks = t % a.KS, tt = t / a.KS;
-      const int nt = a.m_major ? tt % a.NT : tt / num_mtiles, mt = a.m_major ? tt / a.NT : tt - nt * num_mtiles;
-      const int e = a.mtiles[2 * mt], row0 = a.mtiles[2 * mt + 1];
-      const int row_end = min(a.offsets[e + 1], a.P);
-      const int kb0 = (int)((int64_t)KB_all * ks / a.KS), kb1 = (int)((int64_t)KB_all * (ks + 1) / a.KS);
-      const int KB = kb1 - kb0;  // K blocks of this work item
+      const Item w = item_of(t);
+      const int nt = w.nt, kb0 = w.kb0, KB = w.KB;
+      // expert, rows and the scales of the first two K blocks: left in shared memory by the scout warp
+      int e = 0, row0 = 0, row_end = 0;
+      float f0 = 0.f, f1 = 0.f, sa1 = 0.f, wa1 = 0.f, wb1 = 0.f;
+      if (!mbar_wait(smem_u32(&sh->head_full), ntile & 1, abort_flag)) ok = false;
+      if (ok) {
+        e = sh->head_rows[0], row0 = sh->head_rows[1], row_end = sh->head_rows[2];
+        // Scale factors f0 = sa[row,kb] * sw_gate[kb], f1 = sa[row,kb] * sw_up[kb]: the products of block kb + 1 are
+        // formed and the values of block kb + 2 are requested while block kb's TMEM loads are in flight.
+        const float sa0 = sh->head_sa[0][rit];
+        f0 = sa0 * sh->head_w[0], f1 = sa0 * sh->head_w[1];
+        sa1 = sh->head_sa[1][rit], wa1 = sh->head_w[2], wb1 = sh->head_w[3];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->head_empty));
+      }
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
       const bool warp_has_rows = row0 + q * 32 < row_end;  // uniform over the warp
+      int w0i, w1i;
+      scale_index(w, e, w0i, w1i);
       // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's TC_CW-column span of half j
       acc2_t acc[2][TC_CW / 2];
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = acc2_zero();
-      // weight-scale addressing: gemm1 s[e, nt, kb] (gate, up); gemm2 s[e, kb, 2*nt + j]; scales are fp32 here.
-      // Indices are rebuilt from a few 32-bit values every K block instead of keeping pointers alive: the epilogue
-      // loop runs at the edge of the register file and a spilled value costs an L2 round trip here.
-      const float* const S0 = reinterpret_cast<const float*>(a.s0);
-      const float* const S1 = (GEMM2 || DENSE) ? S0 : reinterpret_cast<const float*>(a.s1);  // one scale tensor
-      const int sstep = GEMM2 ? nH : 1;
-      const int nIs = (a.I + kBlock - 1) / kBlock;  // scale rows of one expert (= nI unless a linear layer's N % 128 != 0)
-      const int64_t w0i = (GEMM2   ? (int64_t)e * nI * nH + 2 * nt
-                           : DENSE ? ((int64_t)e * nIs + 2 * nt) * nH
-                                   : ((int64_t)e * nI + nt) * nH) +
-                          (int64_t)kb0 * sstep;
-      const int64_t w1i = w0i + (GEMM2 ? ((2 * nt + 1 < nH) ? 1 : 0) : DENSE ? ((2 * nt + 1 < nIs) ? nH : 0) : 0);
       auto load_sa = [&](int kb) { return valid ? a.as_t[(int64_t)(kb0 + kb) * a.ld + grow] : 0.f; };
-      // Scale factors f0 = sa[row,kb] * sw_gate[kb], f1 = sa[row,kb] * sw_up[kb]: the products of block kb + 1 are
-      // formed and the values of block kb + 2 are requested while block kb's TMEM loads are in flight.
-      float f0, f1, sa1 = 0.f, wa1 = 0.f, wb1 = 0.f;
-      {
-        const float sa0 = load_sa(0);
-        f0 = sa0 * S0[w0i], f1 = sa0 * S1[w1i];
-        if (KB > 1) sa1 = load_sa(1), wa1 = S0[w0i + sstep], wb1 = S1[w1i + sstep];
-      }
       if (!warp_has_rows) {
         // decode-size batches: most row quarters hold no rows; such a warp only hands every buffer straight back
         for (int kb = 0; kb < KB && ok; ++kb, ++it) {
@@ -316,8 +387,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           const float nf0 = sa1 * wa1, nf1 = sa1 * wb1;  // block kb + 1
           if (kb + 2 < KB) {
             sa1 = load_sa(kb + 2);
-            wa1 = S0[w0i + (int64_t)(kb + 2) * sstep];
-            wb1 = S1[w1i + (int64_t)(kb + 2) * sstep];
+            wa1 = S0[w0i + (kb + 2) * sstep];
+            wb1 = S1[w1i + (kb + 2) * sstep];
           }
           tc_ld_wait(s0, s1);
 #pragma unroll
@@ -390,69 +461,79 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           break;
         }
       }
+      // Results leave through shared memory.  A thread owns one row, so stores from registers would put 16 bytes per
+      // lane into 32 different rows per instruction: half-used sectors (and, to a peer, 32 small packets), which cost
+      // several thousand cycles per tile.  Each warp turns its own 32 rows x TC_CW columns through a private patch of
+      // shared memory instead (16-byte chunks, XOR-swizzled so that neither side has bank conflicts; only warp-level
+      // synchronisation) and then stores whole 64- or 128-byte row segments per group of lanes.
+      static_assert(TC_CW == 64, "the row-segment stores below are laid out for 64 columns per warp");
+      const int wepi = warp - 4;
       if (MODE == 0) {
 #pragma unroll
         for (int o = 0; o < TC_CG; ++o) amax = fmaxf(amax, reinterpret_cast<const float*>(sh->ostage)[((ntile & 1) * TC_CG + o) * 128 + rit]);
         amax = fmaxf(amax, kAmaxFloor);
         const float inv = kFp8Max / amax;
-        if (valid) {
-          uint4* dst = reinterpret_cast<uint4*>(a.hq + (int64_t)grow * a.I + nt * 128 + cg * TC_CW);
+        uint4* wst = reinterpret_cast<uint4*>(sh->ostage + 4096 + wepi * 2048);  // 32 rows x 64 B, past the row maxima
 #pragma unroll
-          for (int v4 = 0; v4 < TC_CW / 16; ++v4) {
-            uint4 o;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        for (int v4 = 0; v4 < TC_CW / 16; ++v4) {
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const float2 p0 = unpack2(acc[0][v4 * 8 + w * 2]), p1 = unpack2(acc[0][v4 * 8 + w * 2 + 1]);
-              ow[w] = moe_f32x4_to_e4m3x4(p0.x * inv, p0.y * inv, p1.x * inv, p1.y * inv);
-            }
-            dst[v4] = o;
+          for (int w4 = 0; w4 < 4; ++w4) {
+            const float2 p0 = unpack2(acc[0][v4 * 8 + w4 * 2]), p1 = unpack2(acc[0][v4 * 8 + w4 * 2 + 1]);
+            ow[w4] = moe_f32x4_to_e4m3x4(p0.x * inv, p0.y * inv, p1.x * inv, p1.y * inv);
           }
-          if (cg == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
+          wst[lane * 4 + (v4 ^ ((lane >> 1) & 3))] = o;
         }
-      } else if (a.row_src) {
-        // Peer output: every row goes to its origin rank (plain peer stores).  A thread owns one row, so storing
-        // from registers would put 16 bytes per lane on the link, 32 rows apart; instead each 128-column half of the
-        // tile is turned through shared memory (16-byte chunks, XOR-swizzled by row so that neither side has bank
-        // conflicts) and a warp stores one row's 256 contiguous bytes per instruction.
-        const int wepi = warp - 4;
-        constexpr int ROWS_PER_WARP = 128 / (4 * TC_CG);
-        // destination of the warp's rows, fetched once and in parallel (lane l: row l of the warp's share); walking
-        // tag -> base pointer -> store row by row would put two dependent loads in front of every store
-        int my_tag = 0;
-        unsigned long long my_base = 0;
-        if (lane < ROWS_PER_WARP && row0 + wepi * ROWS_PER_WARP + lane < row_end) {
-          my_tag = a.row_src[row0 + wepi * ROWS_PER_WARP + lane];
-          my_base = a.out_tbl[my_tag >> 24];
+        if (valid && cg == 0) a.hs_t[(int64_t)nt * a.ld + grow] = amax / kFp8Max;
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // 8 rows x 64 B per instruction
+          const int r = i * 8 + (lane >> 2), c = lane & 3;
+          const int orow = row0 + q * 32 + r;
+          if (orow < row_end)
+            *reinterpret_cast<uint4*>(a.hq + (int64_t)orow * a.I + nt * 128 + cg * TC_CW + c * 16) = wst[r * 4 + (c ^ ((r >> 1) & 3))];
         }
+        __syncwarp();
+      } else if (a.row_src || (a.KS == 1 && !a.comb32 && !(DENSE && a.out32))) {
+        // bf16 result rows, to this GPU's output (row r of the tile -> out[row_map[r]]) or, under expert parallelism,
+        // to the rank that owns the token (plain peer stores)
+        const int OUTW = DENSE ? a.I : a.H;  // columns of an output row
+        unsigned long long my_dst = 0;       // byte address of this lane's output row; 0 = the lane has no row
+        if (valid) {
+          if (a.row_src) {
+            const int tag = a.row_src[grow];  // origin of the row: rank << 24 | row
+            my_dst = a.out_tbl[tag >> 24] + (unsigned long long)(tag & 0xFFFFFF) * OUTW * 2;
+          } else {
+            my_dst = reinterpret_cast<unsigned long long>(a.out) + (unsigned long long)(a.row_map ? a.row_map[grow] : grow) * OUTW * 2;
+          }
+        }
+        uint4* wst = reinterpret_cast<uint4*>(sh->ostage + wepi * 4096);  // 32 rows x 128 B
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          const int col0 = nt * 256 + j * 128;
-          if (col0 >= a.H) break;  // uniform
-          uint4* st16 = reinterpret_cast<uint4*>(sh->ostage);
+          const int col0 = nt * 256 + j * 128 + cg * TC_CW;
+          if (col0 < OUTW) {  // uniform over the warp (a linear layer's last tile may be narrower)
 #pragma unroll
-          for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+            for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
+              uint4 o;
+              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const float2 v = unpack2(acc[j][v4 * 4 + w]);
-              o2[w] = __floats2bfloat162_rn(v.x, v.y);
+              for (int w4 = 0; w4 < 4; ++w4) {
+                const float2 v = unpack2(acc[j][v4 * 4 + w4]);
+                o2[w4] = __floats2bfloat162_rn(v.x, v.y);
+              }
+              wst[lane * 8 + (v4 ^ (lane & 7))] = o;
             }
-            const int chunk = cg * (TC_CW / 8) + v4;
-            st16[rit * 16 + (chunk ^ (rit & 15))] = o;
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {  // 4 rows x 128 B per instruction
+              const int r = i * 4 + (lane >> 3), c = lane & 7;
+              const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, r);
+              const uint4 v = wst[r * 8 + (c ^ (r & 7))];
+              if (dst) *reinterpret_cast<uint4*>(dst + (unsigned long long)(col0 + c * 8) * 2) = v;
+            }
+            __syncwarp();
           }
-          asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
-          const uint2* st8 = reinterpret_cast<const uint2*>(sh->ostage);
-          for (int rr = 0; rr < ROWS_PER_WARP; ++rr) {
-            const int r = wepi * ROWS_PER_WARP + rr;
-            if (row0 + r >= row_end) break;  // uniform: rows of a tile are a prefix
-            const int tag = __shfl_sync(0xffffffffu, my_tag, rr);
-            __nv_bfloat16* obase = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, my_base, rr));
-            const uint2 v = st8[(r * 16 + ((lane >> 1) ^ (r & 15))) * 2 + (lane & 1)];
-            *reinterpret_cast<uint2*>(obase + (int64_t)(tag & 0xFFFFFF) * a.H + col0 + lane * 4) = v;
-          }
-          asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
         }
       } else if (valid && a.comb32) {
         // Fused weighted combine: the k rows of one token come from different experts, i.e. from different CTAs, so they
@@ -474,8 +555,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
         }
       } else if (valid) {
+        // fp32 targets: K-split partial sums, or a linear layer's fp32 output
         const int64_t dstrow = a.row_map ? a.row_map[grow] : grow;
-        __nv_bfloat16* obase = a.out;
         const int OUTW = DENSE ? a.I : a.H;  // columns of an output row
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -495,19 +576,6 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             for (int v4 = 0; v4 < TC_CW / 4; ++v4) {
               const float2 p0 = unpack2(acc[j][v4 * 2]), p1 = unpack2(acc[j][v4 * 2 + 1]);
               dst[v4] = make_float4(p0.x, p0.y, p1.x, p1.y);
-            }
-          } else if (col < OUTW) {
-            uint4* dst = reinterpret_cast<uint4*>(obase + dstrow * OUTW + col);
-#pragma unroll
-            for (int v4 = 0; v4 < TC_CW / 8; ++v4) {
-              uint4 o;
-              __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-              for (int w = 0; w < 4; ++w) {
-                const float2 v = unpack2(acc[j][v4 * 4 + w]);
-                o2[w] = __floats2bfloat162_rn(v.x, v.y);
-              }
-              dst[v4] = o;
             }
           }
         }
@@ -575,6 +643,7 @@ template <int MODE>
 int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
   constexpr bool GEMM2 = MODE == 1, DENSE = MODE == 2;
   if (g.scale_dtype != B200MOE_F32) return B200MOE_EINVAL;  // the caller converts bf16 scales first
+  if ((int64_t)g.E * ((g.I + kBlock - 1) / kBlock) * (g.H / kBlock) >= (int64_t(1) << 31)) return B200MOE_EINVAL;  // 32-bit scale indices
   const int K = GEMM2 ? g.I : g.H;
   CUtensorMap tmA, tmB0, tmB1;
   if (!make_map_u8(&tmA, g.aq, (uint64_t)g.P, (uint64_t)K)) return B200MOE_EDRIVER;
