@@ -61,7 +61,7 @@ struct TcShared {
   uint64_t head_full, head_empty;  // one-slot hand-over of a work item's starting values (scout warp -> epilogue warps)
   uint32_t tmem_base;
   int abort_flag;
-  int head_rows[4];        // expert, first row, end of the expert's rows
+  int head_item[8];        // expert, first row, end of the expert's rows, n-tile, first K block, K blocks
   float head_w[4];         // weight scales of the item's first two K blocks: (gate|half 0, up|half 1) x 2
   float head_sa[2][128];   // activation scales of the first two K blocks, per row of the tile
   // results on their way to row-segment stores, one private patch per epilogue warp (down GEMM: 32 rows x 128 B at
@@ -300,7 +300,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         ok = false;
         break;
       }
-      if (lane == 0) sh->head_rows[0] = e, sh->head_rows[1] = row0, sh->head_rows[2] = row_end;
+      if (lane == 0) {
+        sh->head_item[0] = e, sh->head_item[1] = row0, sh->head_item[2] = row_end;
+        sh->head_item[3] = w.nt, sh->head_item[4] = w.kb0, sh->head_item[5] = w.KB;
+      }
       if (lane < 4) sh->head_w[lane] = wv;
 #pragma unroll
       for (int i = 0; i < 4; ++i) sh->head_sa[0][i * 32 + lane] = sa[0][i], sh->head_sa[1][i * 32 + lane] = sa[1][i];
@@ -316,14 +319,15 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     bool ok = true;
     int ntile = 0;  // work items this CTA has finished
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++ntile) {
-      const Item w = item_of(t);
-      const int nt = w.nt, kb0 = w.kb0, KB = w.KB;
-      // expert, rows and the scales of the first two K blocks: left in shared memory by the scout warp
+      // the item (its integer divisions included), its expert and rows and the scales of its first two K blocks: left
+      // in shared memory by the scout warp
+      Item w{0, 0, 0, 0};
       int e = 0, row0 = 0, row_end = 0;
       float f0 = 0.f, f1 = 0.f, sa1 = 0.f, wa1 = 0.f, wb1 = 0.f;
       if (!mbar_wait(smem_u32(&sh->head_full), ntile & 1, abort_flag)) ok = false;
       if (ok) {
-        e = sh->head_rows[0], row0 = sh->head_rows[1], row_end = sh->head_rows[2];
+        e = sh->head_item[0], row0 = sh->head_item[1], row_end = sh->head_item[2];
+        w.nt = sh->head_item[3], w.kb0 = sh->head_item[4], w.KB = sh->head_item[5];
         // Scale factors f0 = sa[row,kb] * sw_gate[kb], f1 = sa[row,kb] * sw_up[kb]: the products of block kb + 1 are
         // formed and the values of block kb + 2 are requested while block kb's TMEM loads are in flight.
         const float sa0 = sh->head_sa[0][rit];
@@ -332,6 +336,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh->head_empty));
       }
+      const int nt = w.nt, kb0 = w.kb0, KB = w.KB;
       const int grow = row0 + rit;
       const bool valid = grow < row_end;
       const bool warp_has_rows = row0 + q * 32 < row_end;  // uniform over the warp
