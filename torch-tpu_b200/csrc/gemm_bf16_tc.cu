@@ -44,6 +44,7 @@ struct BtShared {
   uint64_t tmem_full[2], tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  alignas(16) uint8_t ostage[4][32 * 128];  // per epilogue warp: 32 rows x 128 B of results on their way to row stores
 };
 constexpr size_t BT_SMEM_BYTES =
     1024 + (size_t)BT_STAGES * BT_STAGE_BYTES + (size_t)BT_BSLOTS * BT_B_BYTES + sizeof(BtShared);
@@ -311,8 +312,26 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
       const uint32_t tb = tmem_base + ((uint32_t)(q * 32) << 16) + buf * 256;
       const bool warp_has_rows = row0 + q * 32 < row_end;
       if (warp_has_rows) {
+        // Results leave through a warp-private patch of shared memory (16-byte chunks, XOR-swizzled by row): a thread
+        // owns one row, so stores from registers would put 16 bytes into 32 different rows per instruction; from
+        // the patch a warp stores four rows' whole 128-byte lines per instruction.
+        uint4* wst = reinterpret_cast<uint4*>(sh->ostage[q]);
+        const int OUTW = GEMM2 ? a.H : a.I;
+        const int64_t dstrow = valid ? (GEMM2 && a.row_map ? a.row_map[grow] : grow) : 0;
+        const unsigned long long my_dst =
+            valid ? reinterpret_cast<unsigned long long>(a.out) + (unsigned long long)dstrow * OUTW * 2 : 0ull;
+        auto store_patch = [&](int col0) {  // 64 columns from column col0 of the output rows
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), c8 = lane & 7;
+            const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, r);
+            const uint4 v = wst[r * 8 + (c8 ^ (r & 7))];
+            if (dst) *reinterpret_cast<uint4*>(dst + (unsigned long long)(col0 + c8 * 8) * 2) = v;
+          }
+          __syncwarp();
+        };
         if (!GEMM2) {
-          __nv_bfloat16* hrow = a.out + (int64_t)grow * a.I + nt * 128;
 #pragma unroll 1
           for (int c = 0; c < 8; ++c) {
             uint32_t g[16], u[16];
@@ -333,34 +352,34 @@ moe_gemm_bf16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
               const __nv_bfloat162 b = __floats2bfloat162_rn(h2[0], h2[1]);
               o[i] = *reinterpret_cast<const uint32_t*>(&b);
             }
-            if (valid) {
-              *reinterpret_cast<uint4*>(hrow + c * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-              *reinterpret_cast<uint4*>(hrow + c * 16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
-            }
+            const int ch = (c & 3) * 2;  // 16-byte chunk of the 128-byte patch row
+            wst[lane * 8 + (ch ^ (lane & 7))] = make_uint4(o[0], o[1], o[2], o[3]);
+            wst[lane * 8 + ((ch + 1) ^ (lane & 7))] = make_uint4(o[4], o[5], o[6], o[7]);
+            if ((c & 3) == 3) store_patch(nt * 128 + (c >> 2) * 64);
           }
         } else {
-          const int64_t dstrow = valid ? (a.row_map ? a.row_map[grow] : grow) : 0;
-          __nv_bfloat16* yrow = a.out + dstrow * a.H + nt * 256;
 #pragma unroll 1
           for (int c = 0; c < 16; c += 2) {
             uint32_t v0[16], v1[16];
             tc_ld_issue(tb + c * 16, v0);
             tc_ld_issue(tb + (c + 1) * 16, v1);
             tc_ld_wait(v0, v1);
+            const int col0 = nt * 256 + (c >> 2) * 64;  // the 64-column round this pair of chunks belongs to
+            if (col0 >= a.H) break;                     // uniform (the last n-tile may be narrower; H % 128 == 0)
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               const uint32_t(&v)[16] = half ? v1 : v0;
-              const int col = nt * 256 + (c + half) * 16;
-              if (!valid || col >= a.H) continue;
               uint32_t o[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
                 const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
                 o[i] = *reinterpret_cast<const uint32_t*>(&b);
               }
-              *reinterpret_cast<uint4*>(yrow + (c + half) * 16) = make_uint4(o[0], o[1], o[2], o[3]);
-              *reinterpret_cast<uint4*>(yrow + (c + half) * 16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+              const int ch = ((c & 2) + half) * 2;
+              wst[lane * 8 + (ch ^ (lane & 7))] = make_uint4(o[0], o[1], o[2], o[3]);
+              wst[lane * 8 + ((ch + 1) ^ (lane & 7))] = make_uint4(o[4], o[5], o[6], o[7]);
             }
+            if (c & 2) store_patch(col0);
           }
         }
       }

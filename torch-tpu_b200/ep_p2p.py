@@ -177,6 +177,19 @@ class P2PFusedMoE:
                                         p(sorted_pair), p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank,
                                         self.cap, p(self.status), st()), "b200moe_ep_dispatch")
         self._mark("dispatch")
+        # The shared expert needs nothing from the peers: it runs between this rank's dispatch and the barrier, so the
+        # wait for the slowest sender passes under it instead of leaving the SMs idle.
+        add = None
+        if layer.shared is not None:                               # local work while the peers' rows arrive
+            if self._static is None:
+                out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
+                ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
+            else:
+                out1 = self._static["shared_out"][:T]
+                ops.experts(out1, x, *layer.shared, self._static["zero_ids"][:T],
+                            workspace=self._static["shared_ws"])
+            add = out1.view(T, H)
+            self._mark("shared")
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
                                         p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier")
@@ -191,17 +204,6 @@ class P2PFusedMoE:
                                                ctypes.c_void_p(base), avail, p(self.status), st()),
                 "b200moe_grouped_mlp_remote")
         self._mark("grouped_mlp")
-        add = None
-        if layer.shared is not None:                               # local work between the two barriers
-            if self._static is None:
-                out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
-                ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
-            else:
-                out1 = self._static["shared_out"][:T]
-                ops.experts(out1, x, *layer.shared, self._static["zero_ids"][:T],
-                            workspace=self._static["shared_ws"])
-            add = out1.view(T, H)
-            self._mark("shared")
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
                                         p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier2")
