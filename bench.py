@@ -183,7 +183,9 @@ def build_ep_layer(wl, T, dev, rank, world, seed=0, transport="p2p"):
                      alloc_workspace=False)
     if transport == "p2p":
         from torch_tpu_b200.ep_p2p import P2PFusedMoE
-        return P2PFusedMoE(layer, E, max_tokens=T)
+        ep = P2PFusedMoE(layer, E, max_tokens=T)
+        ep.shared_ctas = int(os.environ.get("B200MOE_EP_SHARED_CTAS", ep.shared_ctas))  # A/B switch, see ep_p2p.py
+        return ep
     from torch_tpu_b200.ep import EPFusedMoE
     return EPFusedMoE(layer, E)
 

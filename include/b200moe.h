@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define B200MOE_ABI_VERSION 2
+#define B200MOE_ABI_VERSION 3
 
 enum {
   B200MOE_OK = 0,
@@ -181,6 +181,9 @@ typedef struct {
   int stages;         /* 0 = the whole call.  Else a mask of B200MOE_STAGE_*: only those stages are enqueued, on
                          a workspace that a whole call with the same sizes and inputs has filled before (how a
                          benchmark times one GEMM alone).  Any other bit is rejected. */
+  int max_ctas;       /* 0 = the tensor-core GEMMs use every SM.  n > 0: their persistent grids are capped at n
+                         CTAs (one per SM), which leaves the other SMs to kernels of another stream - how the
+                         expert-parallel step runs the shared expert beside its dispatch phase. */
 } b200moe_experts_desc;
 
 size_t b200moe_experts_workspace_bytes(const b200moe_experts_desc* d);

@@ -28,7 +28,7 @@ def test_every_declared_symbol_is_exported(m):
     for name in sorted(declared):
         assert hasattr(l, name), f"{name} declared in include/b200moe.h but not exported"
     assert declared == set(m.lib.SIGNATURES), "ctypes binding and header disagree"
-    assert l.b200moe_abi_version() == m.lib.ABI_VERSION == 2
+    assert l.b200moe_abi_version() == m.lib.ABI_VERSION == 3
     assert b"workspace" in l.b200moe_error_string(-3)
 
 

@@ -138,6 +138,7 @@ int check_desc(const b200moe_experts_desc* d) {
   MOE_CHECK_ARG(d->impl_gate_up >= B200MOE_IMPL_AUTO && d->impl_gate_up <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG(d->impl_down >= B200MOE_IMPL_AUTO && d->impl_down <= B200MOE_IMPL_TCGEN05);
   MOE_CHECK_ARG((d->stages & ~B200MOE_STAGE_ALL) == 0);
+  MOE_CHECK_ARG(d->max_ctas >= 0);
   MOE_CHECK_ARG(d->weights_bf16 == 0 || d->weights_bf16 == 1);
   if (d->weights_bf16)
     MOE_CHECK_ARG(d->act_mode == B200MOE_ACT_W8A16 && d->impl != B200MOE_IMPL_SIMPLE &&
@@ -265,6 +266,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
   g.num_mtiles = I32(L.nmt);
   g.offsets = I32(L.offsets);
   g.max_mtiles = L.max_mtiles;
+  g.max_ctas = d->max_ctas;
   g.P = L.P;
   g.H = (int)d->H;
   g.I = (int)d->I;
@@ -363,6 +365,7 @@ extern "C" int b200moe_experts(void* out, const void* x, const void* w_gate, con
     s.num_mtiles = I32(L.s_nmt);
     s.offsets = I32(L.s_offsets);
     s.max_mtiles = L.s_max_mtiles;
+    s.max_ctas = d->max_ctas;
     s.P = d->T;
     s.I = (int)d->I_shared;
     s.E = 1;

@@ -465,7 +465,7 @@ int launch_bt(const MoeGemmArgs& g, cudaStream_t st) {
     attr_set[dev] = true;
   }
   const long long max_tiles = (long long)g.max_mtiles * a.NT;
-  const int sms = moe_device_sm_count();
+  const int sms = g.max_ctas > 0 && g.max_ctas < moe_device_sm_count() ? g.max_ctas : moe_device_sm_count();
   const int grid = (int)(max_tiles < sms ? max_tiles : sms);
   moe_gemm_bf16_tc_kernel<GEMM2><<<grid, BT_THREADS, BT_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
   return moe_launch_status();

@@ -59,11 +59,13 @@ struct TcShared {
                               // accumulator buffer may be read (one tcgen05.commit per K block serves both)
   uint64_t tmem_empty[2];
   uint64_t head_full, head_empty;  // one-slot hand-over of a work item's starting values (scout warp -> epilogue warps)
+  uint64_t dst_full, dst_empty;    // same for the destinations of the item's result rows (taken at the item's END)
   uint32_t tmem_base;
   int abort_flag;
   int head_item[8];        // expert, first row, end of the expert's rows, n-tile, first K block, K blocks
   float head_w[4];         // weight scales of the item's first two K blocks: (gate|half 0, up|half 1) x 2
   float head_sa[2][128];   // activation scales of the first two K blocks, per row of the tile
+  int head_dst[128];       // bf16 result rows: destination row (or origin tag) of every row of the tile, -1 = no row
   // results on their way to row-segment stores, one private patch per epilogue warp (down GEMM: 32 rows x 128 B at
   // warp * 4096; gate/up GEMM: 32 rows x 64 B at 4096 + warp * 2048, behind the row maxima that the epilogue's column
   // groups exchange, float [2][TC_CG][128])
@@ -149,6 +151,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
     mbar_init(smem_u32(&sh->head_full), 1);
     mbar_init(smem_u32(&sh->head_empty), 4 * TC_CG);
+    mbar_init(smem_u32(&sh->dst_full), 1);
+    mbar_init(smem_u32(&sh->dst_empty), 4 * TC_CG);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -192,6 +196,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     w0i = (GEMM2 ? e * nI * nH + 2 * w.nt : DENSE ? (e * nIs + 2 * w.nt) * nH : (e * nI + w.nt) * nH) + w.kb0 * sstep;
     w1i = w0i + (GEMM2 ? ((2 * w.nt + 1 < nH) ? 1 : 0) : DENSE ? ((2 * w.nt + 1 < nIs) ? nH : 0) : 0);
   };
+  // results are bf16 rows stored to row_map / row_src destinations (uniform over the launch)
+  const bool rows_out = MODE != 0 && (a.row_src || (a.KS == 1 && !a.comb32 && !(DENSE && a.out32)));
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TC_REG_LO));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer (one thread)
@@ -293,6 +299,14 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         sa[0][i] = row < row_end ? a.as_t[(int64_t)w.kb0 * a.ld + row] : 0.f;
         sa[1][i] = row < row_end && w.KB > 1 ? a.as_t[(int64_t)(w.kb0 + 1) * a.ld + row] : 0.f;
       }
+      int dst[4] = {-1, -1, -1, -1};  // where the item's result rows go (down GEMM / linear layer with bf16 rows out)
+      if (rows_out) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int row = row0 + i * 32 + lane;
+          if (row < row_end) dst[i] = a.row_src ? a.row_src[row] : a.row_map ? a.row_map[row] : row;
+        }
+      }
       float wv = 0.f;  // lanes 0..3: S0[w0i], S1[w1i], S0[w0i + sstep], S1[w1i + sstep]
       if (lane < 2 || (lane < 4 && w.KB > 1)) wv = ((lane & 1) ? S1 : S0)[((lane & 1) ? w1i : w0i) + ((lane >> 1) ? sstep : 0)];
       // the slot is free once every epilogue warp has taken item n - 1 out of it
@@ -309,6 +323,18 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       for (int i = 0; i < 4; ++i) sh->head_sa[0][i * 32 + lane] = sa[0][i], sh->head_sa[1][i * 32 + lane] = sa[1][i];
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->head_full));
+      if (rows_out) {
+        // (free once every epilogue warp has stored item n - 1: this wait ends at the END of that item, after the
+        // head of item n went out above, so neither hand-over holds the other up)
+        if (n > 0 && !mbar_wait(smem_u32(&sh->dst_empty), (n - 1) & 1, abort_flag)) {
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sh->head_dst[i * 32 + lane] = dst[i];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->dst_full));
+      }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue (4 * TC_CG warps)
@@ -343,14 +369,18 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int w0i, w1i;
       scale_index(w, e, w0i, w1i);
       // accumulators as packed fp32 pairs: acc[j][p] = columns (2p, 2p+1) of this thread's TC_CW-column span of half j
+      // (cleared below, under the first tensor-memory loads of the item)
       acc2_t acc[2][TC_CW / 2];
+      auto clear_acc = [&]() {
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = acc2_zero();
+          for (int i = 0; i < TC_CW / 2; ++i) acc[j][i] = acc2_zero();
+      };
       auto load_sa = [&](int kb) { return valid ? a.as_t[(int64_t)(kb0 + kb) * a.ld + grow] : 0.f; };
       if (!warp_has_rows) {
         // decode-size batches: most row quarters hold no rows; such a warp only hands every buffer straight back
+        clear_acc();
         for (int kb = 0; kb < KB && ok; ++kb, ++it) {
           if (!mbar_wait(smem_u32(&sh->empty[it % TC_STAGES]), (it / TC_STAGES) & 1, abort_flag)) {
             ok = false;
@@ -385,6 +415,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           tc_ld_issue(chunk_addr(tb, 0), s0);
           tc_ld_issue(chunk_addr(tb, 1), s1);
         }
+        clear_acc();
         for (int kb = 0; kb < KB && ok; ++kb, ++it) {
           const bool more = kb + 1 < KB;
           const uint32_t tb = lane_base + (it & 1) * 256;
@@ -435,6 +466,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           }
           f0 = nf0, f1 = nf1;
         }
+      } else {
+        clear_acc();  // (a wait ran out: nothing below stores anything, but nothing reads an unset register either)
       }
       float amax = 0.f;
       if (MODE == 0) {
@@ -504,14 +537,18 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
         // bf16 result rows, to this GPU's output (row r of the tile -> out[row_map[r]]) or, under expert parallelism,
         // to the rank that owns the token (plain peer stores)
         const int OUTW = DENSE ? a.I : a.H;  // columns of an output row
-        unsigned long long my_dst = 0;       // byte address of this lane's output row; 0 = the lane has no row
-        if (valid) {
-          if (a.row_src) {
-            const int tag = a.row_src[grow];  // origin of the row: rank << 24 | row
-            my_dst = a.out_tbl[tag >> 24] + (unsigned long long)(tag & 0xFFFFFF) * OUTW * 2;
-          } else {
-            my_dst = reinterpret_cast<unsigned long long>(a.out) + (unsigned long long)(a.row_map ? a.row_map[grow] : grow) * OUTW * 2;
-          }
+        // destination of this lane's row: fetched by the scout warp (origin tag rank << 24 | row under expert
+        // parallelism, else the output row; -1 = the lane has no row)
+        unsigned long long my_dst = 0;  // byte address of this lane's output row; 0 = the lane has no row
+        if (mbar_wait(smem_u32(&sh->dst_full), ntile & 1, abort_flag)) {
+          const int tag = sh->head_dst[rit];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->dst_empty));
+          if (tag >= 0)
+            my_dst = a.row_src ? a.out_tbl[tag >> 24] + (unsigned long long)(tag & 0xFFFFFF) * OUTW * 2
+                               : reinterpret_cast<unsigned long long>(a.out) + (unsigned long long)tag * OUTW * 2;
+        } else {
+          ok = false;  // (the flag is up: every warp leaves at the next item's barrier; nothing is stored here)
         }
         uint4* wst = reinterpret_cast<uint4*>(sh->ostage + wepi * 4096);  // 32 rows x 128 B
 #pragma unroll
@@ -700,7 +737,8 @@ int launch_tc(const MoeGemmArgs& g, cudaStream_t st) {
     di->attr_set = true;
   }
   const long long max_tiles = (long long)g.max_mtiles * a.NT * a.KS;
-  const int grid = (int)(max_tiles < device_sm_count() ? max_tiles : device_sm_count());
+  const int sms = g.max_ctas > 0 && g.max_ctas < device_sm_count() ? g.max_ctas : device_sm_count();
+  const int grid = (int)(max_tiles < sms ? max_tiles : sms);
   moe_gemm_tc_kernel<MODE><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(tmA, tmB0, tmB1, a);
   return moe_launch_status();
 }

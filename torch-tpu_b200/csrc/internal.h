@@ -25,6 +25,7 @@ struct MoeGemmArgs {
   const int32_t* num_mtiles;
   const int32_t* offsets;   // expert_offsets[E+1]
   int max_mtiles;
+  int max_ctas;             // 0 = all SMs; else the cap on the tensor-core kernels' persistent grid
   int64_t P;
   int H, I, E;
   // outputs

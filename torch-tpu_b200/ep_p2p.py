@@ -139,6 +139,10 @@ class P2PFusedMoE:
         self.epoch_dev = None      # device-side epoch counter: set by enable_graphs(), see there
         self._static = None        # buffers of the allocation-free (graph-capturable) form of forward()
         self.phase_events = None   # set to [] to have forward() record (name, event) after every phase
+        # > 0: the shared expert runs on a side stream beside routing and dispatch, its GEMMs capped at this many
+        # CTAs (the dispatch is bound by the links and needs few SMs); 0: in line, on every SM, after the dispatch
+        self.shared_ctas = 0
+        self._side = None
 
     def _next_epoch(self):
         self.epoch = (self.epoch + 1) & 0xFFFFFFFF
@@ -159,6 +163,25 @@ class P2PFusedMoE:
         N, rank, E = self.N, self.rank, self.E
         p, st = ops._ptr, ops._stream
         self._mark("start")
+        add, out1 = None, None
+        if layer.shared is not None:                               # buffers of the shared expert's pass
+            if self._static is None:
+                out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
+                ids0 = torch.zeros(T, 1, dtype=torch.int32, device=x.device)
+                shared_ws = None
+            else:
+                out1, ids0, shared_ws = (self._static["shared_out"][:T], self._static["zero_ids"][:T],
+                                         self._static["shared_ws"])
+        beside = layer.shared is not None and self.shared_ctas > 0
+        if beside:
+            # The shared expert needs nothing but x: it runs beside routing, permutation and dispatch on part of the
+            # SMs (a fork/join of two streams, capturable); the grouped GEMMs, which want every SM, wait for it.
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.dev)
+            self._side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._side):
+                ops.experts(out1, x, *layer.shared, ids0, workspace=shared_ws, max_ctas=self.shared_ctas)
+            add = out1.view(T, H)
         ids, w = layer.route(x)                                    # ids over GLOBAL experts
         if self._static is None:
             sorted_pair, offsets = ops.permute(ids, E, status=self.status)
@@ -177,22 +200,18 @@ class P2PFusedMoE:
                                         p(sorted_pair), p(ids), p(offsets), p(self.dst_row0), T, self.k, H, E, N, rank,
                                         self.cap, p(self.status), st()), "b200moe_ep_dispatch")
         self._mark("dispatch")
-        # The shared expert needs nothing from the peers: it runs between this rank's dispatch and the barrier, so the
-        # wait for the slowest sender passes under it instead of leaving the SMs idle.
-        add = None
-        if layer.shared is not None:                               # local work while the peers' rows arrive
-            if self._static is None:
-                out1 = torch.empty(T, 1, H, dtype=torch.bfloat16, device=x.device)
-                ops.experts(out1, x, *layer.shared, torch.zeros(T, 1, dtype=torch.int32, device=x.device))
-            else:
-                out1 = self._static["shared_out"][:T]
-                ops.experts(out1, x, *layer.shared, self._static["zero_ids"][:T],
-                            workspace=self._static["shared_ws"])
+        if layer.shared is not None and not beside:
+            # in line: between this rank's dispatch and the barrier, so that the wait for the slowest sender passes
+            # under it instead of leaving the SMs idle
+            ops.experts(out1, x, *layer.shared, ids0, workspace=shared_ws)
             add = out1.view(T, H)
             self._mark("shared")
         L.check(lib.b200moe_p2p_barrier(p(a.table("flags")), N, rank, self._next_epoch(), p(self.epoch_dev),
                                         p(self.status), st()), "b200moe_p2p_barrier")
         self._mark("barrier")
+        if beside:
+            torch.cuda.current_stream().wait_stream(self._side)
+            self._mark("shared (join)")
         L.check(lib.b200moe_ep_transpose_scales(p(self.xs), self.ld, p(self.xs_rows), p(self.recv_offsets[self.El:]),
                                                 H, self.cap, st()), "b200moe_ep_transpose_scales")
         wg, wu, wd, sg, su, sd = layer.w

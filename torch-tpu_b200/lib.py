@@ -10,7 +10,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libb200moe.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 OK, EINVAL, ESHAPE, EWORKSPACE, EALIGN, EDRIVER = 0, -1, -2, -3, -4, -5
 F32, BF16, F16 = 0, 1, 2
 SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
@@ -25,7 +25,7 @@ class ExpertsDesc(Structure):
     _fields_ = [("T", c_int64), ("H", c_int64), ("I", c_int64), ("E", c_int64), ("k", c_int64),
                 ("I_shared", c_int64), ("out_mode", c_int), ("act_mode", c_int), ("impl", c_int),
                 ("scale_dtype", c_int), ("w_dtype", c_int), ("impl_gate_up", c_int), ("impl_down", c_int),
-                ("weights_bf16", c_int), ("stages", c_int)]
+                ("weights_bf16", c_int), ("stages", c_int), ("max_ctas", c_int)]
 
 
 # name -> (restype, argtypes): every symbol include/b200moe.h declares

@@ -116,9 +116,9 @@ def quant_rows(x, row_map=None, div=1):
 
 def make_desc(T, H, I, E, k, *, I_shared=0, out_mode=L.OUT_PER_SLOT, act_mode=L.ACT_W8A8, impl=L.IMPL_AUTO,
               scale_dtype=torch.float32, w_dtype=torch.float32, impl_gate_up=L.IMPL_AUTO, impl_down=L.IMPL_AUTO,
-              weights_bf16=False, stages=0):
+              weights_bf16=False, stages=0, max_ctas=0):
     return L.ExpertsDesc(T, H, I, E, k, I_shared, out_mode, act_mode, impl, _DT[scale_dtype], _DT[w_dtype],
-                         impl_gate_up, impl_down, int(weights_bf16), stages)
+                         impl_gate_up, impl_down, int(weights_bf16), stages, max_ctas)
 
 
 def experts_workspace_bytes(desc):
@@ -127,12 +127,13 @@ def experts_workspace_bytes(desc):
 
 def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, act_mode=L.ACT_W8A8,
             impl=L.IMPL_AUTO, workspace=None, status=None, fused_combine=False, impl_gate_up=L.IMPL_AUTO,
-            impl_down=L.IMPL_AUTO, stages=0):
+            impl_down=L.IMPL_AUTO, stages=0, max_ctas=0):
     """Everything after routing (reference op my_ops.fused_moe_fused_experts, my_ops/fusedMoE.cpp:117-236).
     ``out`` [T,k,H] -> un-weighted per-slot rows; ``out`` [T,H] -> weighted combine with ``topk_w`` (+ ``shared`` =
     (wg,wu,wd,sg,su,sd) of a dense expert applied to every token), formed by a separate kernel in slot order or,
     with ``fused_combine``, inside the down GEMM's epilogue (fp32 reductions, order not fixed).  ``stages``: a
-    mask of ``L.STAGE_*`` to re-run part of a call on a workspace that a whole call has filled.  Returns ``out``."""
+    mask of ``L.STAGE_*`` to re-run part of a call on a workspace that a whole call has filled.  ``max_ctas`` > 0
+    caps the tensor-core kernels' persistent grids (SMs left to another stream's kernels).  Returns ``out``."""
     _chk(out, "out", torch.bfloat16)
     _chk(x, "x", torch.bfloat16)
     bf16w = wg.dtype == torch.bfloat16      # bf16 weights carry no scales: sg/su/sd may be None
@@ -152,7 +153,8 @@ def experts(out, x, wg, wu, wd, sg, su, sd, ids, topk_w=None, *, shared=None, ac
     d = make_desc(T, H, I, E, k, I_shared=I_shared, out_mode=out_mode, act_mode=act_mode, impl=impl,
                   scale_dtype=torch.float32 if bf16w else sg.dtype,
                   w_dtype=topk_w.dtype if topk_w is not None else torch.float32,
-                  impl_gate_up=impl_gate_up, impl_down=impl_down, weights_bf16=bf16w, stages=stages)
+                  impl_gate_up=impl_gate_up, impl_down=impl_down, weights_bf16=bf16w, stages=stages,
+                  max_ctas=max_ctas)
     need = experts_workspace_bytes(d)
     if need == 0 and T > 0:
         raise ValueError("unsupported sizes for b200moe_experts (H, I multiples of 128; see include/b200moe.h)")
