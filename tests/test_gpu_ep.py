@@ -51,7 +51,7 @@ def _run_rank(rank, world, port, q, mode):
         layer = FusedMoE(cfg, wr.to(dev), *local, bias=bias.to(dev), shared=tuple(t.to(dev) for t in shared),
                          max_tokens=256, alloc_workspace=False)
         bad = mode.endswith("_badids")
-        beside = mode.endswith("_beside")    # shared expert on a side stream with a capped grid, beside the dispatch
+        inline = mode.endswith("_inline")    # shared expert in line (default: on a side stream beside the dispatch)
         mode = mode.split("_")[0]
         if bad:
             # expert ids outside [0,E) reach the exchange: those (token,slot) pairs must be skipped everywhere
@@ -70,8 +70,8 @@ def _run_rank(rank, world, port, q, mode):
         if mode == "p2p":
             from torch_tpu_b200.ep_p2p import P2PFusedMoE
             ep = P2PFusedMoE(layer, E, max_tokens=256)
-            if beside:
-                ep.shared_ctas = 64
+            if inline:
+                ep.shared_ctas = 0
             ep(x[:40].to(dev))             # a first call of another size: epochs and buffers are reused after it
             y = ep(x.to(dev)).clone()
             torch.cuda.synchronize()
@@ -108,7 +108,7 @@ def _run_rank(rank, world, port, q, mode):
 
 
 @pytest.mark.parametrize("world,mode", [(1, "nccl"), (2, "nccl"), (1, "p2p"), (2, "p2p"), (1, "nccl_badids"),
-                                        (1, "p2p_badids"), (2, "p2p_badids"), (1, "p2p_beside"), (2, "p2p_beside")])
+                                        (1, "p2p_badids"), (2, "p2p_badids"), (1, "p2p_inline"), (2, "p2p_inline")])
 def test_ep_cuda_path(world, mode):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
