@@ -218,3 +218,25 @@ def test_bf16_weight_experts_multi_tile(m):
     y = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
     m.ops.experts(y, x.to(DEV), w0.to(DEV), w1.to(DEV), wd.to(DEV), None, None, None, ids.to(DEV), w.to(DEV))
     _check(y, (want.float() * w[..., None]).sum(1), "bf16-weight experts, combined")
+
+
+def test_capped_grid_gives_the_same_result(m):
+    """``max_ctas`` only changes how many persistent CTAs walk the work items: at a size without K split the
+    result is the same to the bit (and every row is written) with 1, 5 or all SMs; a negative cap is refused."""
+    L = m.lib
+    T, H, I, E, k = 700, 512, 256, 8, 2
+    p = small_problem(T, H, I, E, k, seed=77)
+    d = to_dev(p)
+    outs = []
+    for cap in (0, 1, 5):
+        out = torch.full((T, k, H), float("nan"), dtype=torch.bfloat16, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        m.ops.experts(out, d["x"], d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"],
+                      impl=L.IMPL_TCGEN05, status=status, max_ctas=cap)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0
+        assert torch.isfinite(out.float()).all()
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    with pytest.raises(Exception):
+        m.ops.experts(outs[0], d["x"], d["wg"], d["wu"], d["wd"], d["sg"], d["su"], d["sd"], d["ids"], max_ctas=-1)

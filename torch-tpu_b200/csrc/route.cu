@@ -201,8 +201,8 @@ route_kernel(int32_t* __restrict__ ids, float* __restrict__ w, __nv_bfloat16* __
 // ---- router GEMM ---------------------------------------------------------------------------------
 // logits[t,e] = sum_h x[t,h] * wr[e,h]; bf16 operands, fp32 accumulation on the warp-level tensor path
 // (mma.sync m16n8k16).  It is ~0.5 % of the layer's FLOPs, so it stays a small, plain kernel: CTA tile
-// 64 tokens x 64 experts, K chunks of 64 staged in shared memory, 4 warps each owning 16 token rows.
-constexpr int RG_BM = 64, RG_BN = 64, RG_BK = 64, RG_LD = RG_BK + 8;  // +8 bf16: conflict-free fragment reads
+// 32 tokens x 64 experts, K chunks of 64 staged in shared memory, 4 warps each owning 16 token rows x 32 experts.
+constexpr int RG_BM = 32, RG_BN = 64, RG_BK = 64, RG_LD = RG_BK + 8, RG_STAGES = 3;  // +8 bf16: conflict-free fragment reads
 
 __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile(
@@ -221,53 +221,63 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, int
 __global__ void __launch_bounds__(128)
 router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__ x,
                    const __nv_bfloat16* __restrict__ wr, int64_t T, int64_t H, int64_t E) {
-  // two stages: the copies of K chunk kt+1 are in flight while the MMAs of chunk kt run
-  __shared__ __align__(16) __nv_bfloat16 sA[2][RG_BM * RG_LD];
-  __shared__ __align__(16) __nv_bfloat16 sB[2][RG_BN * RG_LD];
+  // Three stages: the copies of K chunks kt+1 and kt+2 are in flight while the MMAs of chunk kt run.  The MMAs of a
+  // chunk are a few hundred cycles and a copy is an L2 round trip, so the kernel lives on copies in flight: tiles
+  // of 32 rows (twice the blocks of a 64-row tile, two or three per SM) and three stages keep about four chunks
+  // per SM on their way.  A sum over K is formed in the same order whatever the tiling: logits do not change.
+  __shared__ __align__(16) __nv_bfloat16 sA[RG_STAGES][RG_BM * RG_LD];
+  __shared__ __align__(16) __nv_bfloat16 sB[RG_STAGES][RG_BN * RG_LD];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp & 1, wn = warp >> 1;  // the warp's 16 rows and 32 columns of the 32 x 64 tile
   const int64_t t0 = (int64_t)blockIdx.x * RG_BM, e0 = (int64_t)blockIdx.y * RG_BN;
-  float acc[RG_BN / 8][4];
+  float acc[4][4];
 #pragma unroll
-  for (int i = 0; i < RG_BN / 8; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
   const int g = lane >> 2, tq = lane & 3;
   auto load_stage = [&](int st, int64_t k0) {
-    // 64 rows x 64 bf16 = 512 chunks of 16 B per operand; 128 threads x 4
+    // A: 32 rows x 64 bf16 = 256 chunks of 16 B (128 threads x 2); B: 64 rows = 512 chunks (x 4)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int c = tid + i * 128;
+      const int r = c >> 3, cc = (c & 7) * 8;
+      const bool ok = k0 + cc < H && t0 + r < T;
+      cp_async16(sA[st] + r * RG_LD + cc, ok ? x + (t0 + r) * H + k0 + cc : x, ok ? 16 : 0);
+    }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int c = tid + i * 128;
       const int r = c >> 3, cc = (c & 7) * 8;
-      const bool ka = k0 + cc < H;
-      const bool oka = ka && t0 + r < T, okb = ka && e0 + r < E;
-      cp_async16(sA[st] + r * RG_LD + cc, oka ? x + (t0 + r) * H + k0 + cc : x, oka ? 16 : 0);
-      cp_async16(sB[st] + r * RG_LD + cc, okb ? wr + (e0 + r) * H + k0 + cc : wr, okb ? 16 : 0);
+      const bool ok = k0 + cc < H && e0 + r < E;
+      cp_async16(sB[st] + r * RG_LD + cc, ok ? wr + (e0 + r) * H + k0 + cc : wr, ok ? 16 : 0);
     }
-    asm volatile("cp.async.commit_group;" ::: "memory");
   };
   const int nk = (int)((H + RG_BK - 1) / RG_BK);
+  // one commit group per chunk, empty where there is no chunk left, so that "all but the two newest groups are
+  // complete" always means "chunk kt has landed"
   load_stage(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  if (nk > 1) load_stage(1, RG_BK);
+  asm volatile("cp.async.commit_group;" ::: "memory");
   for (int kt = 0; kt < nk; ++kt) {
-    const int st = kt & 1;
-    if (kt + 1 < nk) {
-      load_stage(st ^ 1, (int64_t)(kt + 1) * RG_BK);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    const int st = kt % RG_STAGES;
+    if (kt + 2 < nk) load_stage((kt + 2) % RG_STAGES, (int64_t)(kt + 2) * RG_BK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 2;" ::: "memory");
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < RG_BK; kk += 16) {
       uint32_t a[4];
-      const __nv_bfloat16* pa = sA[st] + (warp * 16 + g) * RG_LD + kk + tq * 2;
+      const __nv_bfloat16* pa = sA[st] + (wm * 16 + g) * RG_LD + kk + tq * 2;
       a[0] = *reinterpret_cast<const uint32_t*>(pa);
       a[1] = *reinterpret_cast<const uint32_t*>(pa + 8 * RG_LD);
       a[2] = *reinterpret_cast<const uint32_t*>(pa + 8);
       a[3] = *reinterpret_cast<const uint32_t*>(pa + 8 * RG_LD + 8);
 #pragma unroll
-      for (int nb = 0; nb < RG_BN / 8; ++nb) {
+      for (int nb = 0; nb < 4; ++nb) {
         uint32_t b[2];
-        const __nv_bfloat16* pb = sB[st] + (nb * 8 + g) * RG_LD + kk + tq * 2;
+        const __nv_bfloat16* pb = sB[st] + (wn * 32 + nb * 8 + g) * RG_LD + kk + tq * 2;
         b[0] = *reinterpret_cast<const uint32_t*>(pb);
         b[1] = *reinterpret_cast<const uint32_t*>(pb + 8);
         mma_bf16_16816(acc[nb], a, b);
@@ -276,8 +286,8 @@ router_gemm_kernel(float* __restrict__ logits, const __nv_bfloat16* __restrict__
     __syncthreads();  // the stage is overwritten by the copies issued at the top of the next iteration
   }
 #pragma unroll
-  for (int nb = 0; nb < RG_BN / 8; ++nb) {
-    int64_t r0 = t0 + warp * 16 + g, c0 = e0 + nb * 8 + tq * 2;
+  for (int nb = 0; nb < 4; ++nb) {
+    int64_t r0 = t0 + wm * 16 + g, c0 = e0 + wn * 32 + nb * 8 + tq * 2;
     if (r0 < T) {
       if (c0 < E) logits[r0 * E + c0] = acc[nb][0];
       if (c0 + 1 < E) logits[r0 * E + c0 + 1] = acc[nb][1];
