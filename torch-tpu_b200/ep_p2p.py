@@ -174,6 +174,18 @@ class P2PFusedMoE:
                 out1, ids0, shared_ws = (self._static["shared_out"][:T], self._static["zero_ids"][:T],
                                          self._static["shared_ws"])
         beside = layer.shared is not None and self.shared_ctas > 0
+        if beside:
+            # The shared expert needs nothing but x: it runs beside routing, permutation and dispatch on part of the
+            # SMs (a fork/join of two streams, capturable); the grouped GEMMs, which want every SM, wait for it.
+            # The fork has to come first: a persistent CTA of the GEMMs needs a whole SM, and once the dispatch's
+            # many small blocks are spread over every SM it finds none until they have drained (forked after the
+            # router, the join waited 0.35 ms for a shared expert that had only started after the dispatch).
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=self.dev)
+            self._side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._side):
+                ops.experts(out1, x, *layer.shared, ids0, workspace=shared_ws, max_ctas=self.shared_ctas)
+            add = out1.view(T, H)
         ids, w = layer.route(x)                                    # ids over GLOBAL experts
         if self._static is None:
             sorted_pair, offsets = ops.permute(ids, E, status=self.status)
@@ -182,17 +194,6 @@ class P2PFusedMoE:
             L.check(lib.b200moe_permute(p(sorted_pair), p(offsets), p(ids), T, self.k, E, p(self._static["scratch"]),
                                         p(self.status), st()), "b200moe_permute")
         self._mark("route+permute")
-        if beside:
-            # The shared expert needs nothing but x: it runs beside the counts exchange, the dispatch and its barrier on
-            # part of the SMs (a fork/join of two streams, capturable); the grouped GEMMs, which want every SM, wait
-            # for it.  It starts after the router, which everything else waits for and which wants every SM itself
-            # (started beside it, the 256-expert router GEMM took three times as long on the SMs left over).
-            if self._side is None:
-                self._side = torch.cuda.Stream(device=self.dev)
-            self._side.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(self._side):
-                ops.experts(out1, x, *layer.shared, ids0, workspace=shared_ws, max_ctas=self.shared_ctas)
-            add = out1.view(T, H)
         L.check(lib.b200moe_ep_exchange_counts(p(a.table("cnt")), p(a.table("flags")), p(offsets), E, N, rank,
                                                self._next_epoch(), p(self.epoch_dev), p(self.status), st()),
                 "b200moe_ep_exchange_counts")
