@@ -106,3 +106,40 @@ def test_invalid_arguments_are_rejected(ops):
         ops.topk(torch.zeros(2, 2048, device=DEV), 8)  # n > 1024
     with pytest.raises(RuntimeError):
         ops.topk(s, 64)                      # k > 32
+
+
+@pytest.mark.parametrize("H,E,k,mode", [(4096, 8, 2, "softmax"), (7168, 256, 8, "deepseek"), (2048, 128, 8, "softmax")])
+def test_router_kernels_agree_across_batch_sizes_at_real_shapes(ops, H, E, k, mode):
+    """The router has three kernels with three summation orders (T <= 16: one block per expert row; E <= 16: a block
+    per 4 tokens; else the tensor-core GEMM), so the same token meets a different kernel in a different batch.
+    Measured here at the benchmark's own hidden sizes, 2048 tokens routed as one batch and 16 at a time:
+    - every kernel agrees with an fp64 product of the same bf16 operands: the CUDA-core kernels to 1e-5, the
+      tensor-core GEMM (fp32 accumulation inside mma.sync) to 2e-5 of the largest logit;
+    - a row whose selection gaps (between consecutive picks, at the top-k boundary and at the group boundary) are all
+      wider than 1e-3 relative gets the same experts in the same order in either batch size, and rows that get another
+      set of experts are below 2 % of the batch."""
+    T_big = 2048
+    x, wr, _ = O.make_inputs(T_big, H, E, seed=H + E, router_std=H ** -0.5)   # logits ~ N(0, 1)
+    xd, wd = x.to(DEV), wr.to(DEV)
+    big = ops.router_logits(xd, wd).cpu()
+    small = torch.cat([ops.router_logits(xd[i:i + 16].contiguous(), wd).cpu() for i in range(0, T_big, 16)])
+    one = torch.cat([ops.router_logits(xd[i:i + 1].contiguous(), wd).cpu() for i in range(4)])
+    ref = x.double() @ wr.double().T
+    scale = float(ref.abs().max())
+    tc = E > 16                                           # the large batch goes through the tensor-core kernel
+    assert float((big.double() - ref).abs().max()) <= (2e-5 if tc else 1e-6) * scale
+    assert float((small.double() - ref).abs().max()) <= 1e-6 * scale
+    assert float((one.double() - ref[:4]).abs().max()) <= 1e-6 * scale
+    if mode == "softmax":
+        wide = O.tie_free_rows(torch.softmax(ref.float(), -1), k, rel_gap=1e-3)
+        route = lambda lg: ops.route(lg.to(DEV), k, "softmax")[0].cpu()
+    else:
+        bias = torch.randn(E, generator=torch.Generator().manual_seed(5)) * 0.01
+        wide = O.tie_free_rows(torch.sigmoid(ref.float()) + bias, k, 8, 4, rel_gap=1e-3)
+        route = lambda lg: ops.route(lg.to(DEV), k, "sigmoid", bias.to(DEV), 8, 4, True, 2.5)[0].cpu()
+    ids_big, ids_small = route(big), route(small)
+    differ = (ids_big != ids_small).any(-1)
+    assert float(wide.float().mean()) > 0.2               # (8 ordered picks of 256 leave few rows with every gap wide)
+    assert not bool((differ & wide).any())                # no row with decidable gaps routes differently
+    other_set = (torch.sort(ids_big, -1)[0] != torch.sort(ids_small, -1)[0]).any(-1)
+    assert float(other_set.float().mean()) <= 0.02        # rows that get another SET of experts in the other batch size
