@@ -73,10 +73,17 @@ permute_scan_kernel(int32_t* __restrict__ chunk_cnt, int nchunks, int E, int32_t
   __shared__ int tmp[kChunk];
   int total = 0;
   if ((int)threadIdx.x < E) {
-    for (int c = 0; c < nchunks; ++c) {
-      int v = chunk_cnt[(int64_t)c * E + threadIdx.x];
-      chunk_cnt[(int64_t)c * E + threadIdx.x] = total;  // becomes chunk_base
-      total += v;
+    // eight counts are requested before the first is used: walked one by one, every chunk costs an L2 round trip
+    // (64 chunks of a 65536-pair batch: 20 us for this one block)
+    for (int c0 = 0; c0 < nchunks; c0 += 8) {
+      int v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = c0 + i < nchunks ? chunk_cnt[(int64_t)(c0 + i) * E + threadIdx.x] : 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (c0 + i < nchunks) chunk_cnt[(int64_t)(c0 + i) * E + threadIdx.x] = total;  // becomes chunk_base
+        total += v[i];
+      }
     }
   }
   block_exclusive_scan(total, E, offsets, tmp);
@@ -183,13 +190,23 @@ quant_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ s_t, int64_t ld,
   if (row_map && row_map[r] < 0) return;  // position of a dropped pair (id out of range): no row
   const int64_t src = row_map ? (int64_t)(row_map[r] / div) : r;
   const __nv_bfloat16* xr = x + src * H;
-  for (int c0 = c_begin; c0 < c_begin + cpw * 256 && c0 < H; c0 += 256) {
-    const int c = c0 + lane * 8;
-    float v[8];
-    float amax = 0.f;
-    if (c < H) {
-      uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
-      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const int c_end = min(c_begin + cpw * 256, H);
+  // Four 256-column chunks at a time, their loads issued before the first is used: taken one by one, every chunk of a
+  // row costs the warp a whole round trip to L2 (Qwen3 shape, 65536 rows of 2048: 73 us for 400 MB).
+  for (int c0 = c_begin; c0 < c_end; c0 += 4 * 256) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * 256 + lane * 8;
+      raw[u] = c < c_end ? *reinterpret_cast<const uint4*>(xr + c) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * 256 + lane * 8;
+      if (c0 + u * 256 >= c_end) break;  // uniform over the warp
+      float v[8];
+      float amax = 0.f;
+      const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float2 f = __bfloat1622float2(b2[i]);
@@ -197,17 +214,17 @@ quant_rows_kernel(uint8_t* __restrict__ q, float* __restrict__ s_t, int64_t ld,
         v[2 * i + 1] = f.y;
         amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
       }
-    }
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (c < H) {
-      amax = fmaxf(amax, kAmaxFloor);
-      const float inv = kFp8Max / amax;
-      uint2 out;
-      out.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
-      out.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
-      *reinterpret_cast<uint2*>(q + r * H + c) = out;
-      if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld + r] = amax / kFp8Max;
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      if (c < c_end) {
+        amax = fmaxf(amax, kAmaxFloor);
+        const float inv = kFp8Max / amax;
+        uint2 out;
+        out.x = moe_f32x4_to_e4m3x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+        out.y = moe_f32x4_to_e4m3x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+        *reinterpret_cast<uint2*>(q + r * H + c) = out;
+        if ((lane & 15) == 0) s_t[(int64_t)(c >> 7) * ld + r] = amax / kFp8Max;
+      }
     }
   }
 }
