@@ -89,7 +89,7 @@ def test_op_surface_matches_reference_names_and_schemas(m):
     want = {
         "fused_moe_fused_experts": 25, "fused_moe_fused_experts_v2": 27, "fused_moe_grouped_topk": 10,
         "noaux_tc_topk": 6, "mlp_w8a16_dq_forward": 9, "mlp_w8a8_quant_forward": 9,
-        "mm_w8a16_dq_forward": 5}
+        "mm_w8a16_dq_forward": 5, "enable_profile": 2, "disable_profile": 0}
     for name, nargs in want.items():
         op = getattr(torch.ops.my_ops, name)
         schema = op.default._schema

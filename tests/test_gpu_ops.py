@@ -202,3 +202,30 @@ def test_scaled_mm_fp8(m, M, K, N):
         # the reference's acceptance test: row-wise cosine >= 0.99 (python/test/_scaled_mm.py:62-65)
         cs = torch.nn.functional.cosine_similarity(out.cpu().double(), want * sa * sb, dim=1)
         assert float(cs.min()) >= 0.99
+
+
+def test_profile_toggles_like_the_reference(m):
+    """enable_profile / disable_profile (torch_tpu/csrc/ops/my_ops/myOps.cpp:67-68; called as
+    torch.ops.my_ops.enable_profile(4096, mode) in python/tgi_test/tgi_modules.py:192): while enabled every op call
+    is timed with CUDA events on the current stream; disable_profile() prints and keeps calls / total / average per op.
+    Calls made while disabled are not counted; max_record_num bounds the timed calls."""
+    z = load("noaux_topk.npz")
+    scores = bf16_from_bits(z["ref_scores_bf16"]).repeat(16, 1).to(DEV)
+    values = torch.empty(16, 8, dtype=scores.dtype, device=DEV)
+    indices = torch.empty(16, 8, dtype=torch.int32, device=DEV)
+    call = lambda: torch.ops.my_ops.noaux_tc_topk(values, indices, scores, 8, 4, 8)
+    call()                                           # not counted: profiling is off
+    torch.ops.my_ops.enable_profile(4096, 1)
+    for _ in range(5):
+        call()
+    torch.ops.my_ops.disable_profile()
+    call()                                           # not counted either
+    rows = [r.strip().split(", ") for r in torch.ops.my_ops.b200_profile_summary().splitlines()[1:]]
+    assert len(rows) == 1 and rows[0][0] == "noaux_tc_topk" and int(rows[0][1]) == 5
+    assert 0.0 < float(rows[0][2]) < 1000.0 and float(rows[0][3]) > 0.0
+    torch.ops.my_ops.enable_profile(2, None)         # only the first two calls are timed
+    for _ in range(4):
+        call()
+    torch.ops.my_ops.disable_profile()
+    rows = [r.strip().split(", ") for r in torch.ops.my_ops.b200_profile_summary().splitlines()[1:]]
+    assert int(rows[0][1]) == 2

@@ -10,13 +10,20 @@
 #include <torch/library.h>
 #include <ATen/ATen.h>
 
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <algorithm>
 #include <initializer_list>
+#include <map>
+#include <sstream>
+#include <string>
 #include <unordered_map>
 #include <utility>
+#include <vector>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "../../include/b200moe.h"
 
@@ -30,6 +37,100 @@ void check_rc(int rc, const char* what) {
 void check_cuda_contig(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+// ---- profiling toggles ------------------------------------------------------------------------------
+// torch.ops.my_ops.enable_profile(max_record_num, mode) / disable_profile(), as the reference registers them
+// (torch_tpu/csrc/ops/my_ops/myOps.cpp:67-68, profile.cpp:12-53: they switch the runtime's per-op profile on the
+// current stream).  Here: while enabled, every op of this library opens an NVTX range under its own name and, with
+// mode bit 0 (the default), brackets its launches with two CUDA events on the current stream; disable_profile()
+// synchronises those events, prints calls / total / average device time per op and keeps the table for
+// my_ops.b200_profile_summary().  At most max_record_num calls are timed (later ones only get their NVTX range).
+struct OpProfile {
+  struct Rec {
+    const char* name;
+    cudaEvent_t a, b;
+  };
+  std::mutex mu;
+  bool on = false;
+  int64_t max_records = 40960, mode = 1;
+  std::vector<Rec> recs;
+  std::string summary;
+};
+OpProfile& op_profile() {
+  static OpProfile p;
+  return p;
+}
+
+struct OpScope {
+  cudaEvent_t b = nullptr;
+  cudaStream_t st = nullptr;
+  bool ranged = false;
+  explicit OpScope(const char* name) {
+    OpProfile& p = op_profile();
+    std::lock_guard<std::mutex> lock(p.mu);
+    if (!p.on) return;
+    nvtxRangePushA(name);
+    ranged = true;
+    if (!(p.mode & 1) || (int64_t)p.recs.size() >= p.max_records) return;
+    cudaEvent_t a = nullptr;
+    if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) {
+      if (a) cudaEventDestroy(a);
+      b = nullptr;
+      return;
+    }
+    st = at::cuda::getCurrentCUDAStream();
+    cudaEventRecord(a, st);
+    p.recs.push_back({name, a, b});
+  }
+  ~OpScope() {
+    if (b) cudaEventRecord(b, st);
+    if (ranged) nvtxRangePop();
+  }
+};
+
+void enable_profile(c10::optional<int64_t> max_record_num, c10::optional<int64_t> mode) {
+  OpProfile& p = op_profile();
+  std::lock_guard<std::mutex> lock(p.mu);
+  for (auto& r : p.recs) {
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  p.recs.clear();
+  p.max_records = max_record_num.has_value() ? std::max<int64_t>(0, *max_record_num) : 40960;
+  p.mode = mode.has_value() ? *mode : 1;
+  p.on = true;
+}
+
+void disable_profile() {
+  OpProfile& p = op_profile();
+  std::lock_guard<std::mutex> lock(p.mu);
+  p.on = false;
+  std::map<std::string, std::pair<int64_t, double>> agg;  // op -> (calls, ms)
+  for (auto& r : p.recs) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(r.b) == cudaSuccess && cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) {
+      auto& e = agg[r.name];
+      e.first += 1;
+      e.second += ms;
+    }
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  p.recs.clear();
+  std::ostringstream os;
+  os << "my_ops profile: op, calls, total ms, average us\n";
+  for (auto& kv : agg)
+    os << "  " << kv.first << ", " << kv.second.first << ", " << kv.second.second << ", "
+       << 1000.0 * kv.second.second / (double)kv.second.first << "\n";
+  p.summary = os.str();
+  std::fputs(p.summary.c_str(), stdout);
+}
+
+std::string b200_profile_summary() {
+  OpProfile& p = op_profile();
+  std::lock_guard<std::mutex> lock(p.mu);
+  return p.summary;
 }
 
 int scale_dtype_of(const Tensor& s) {
@@ -266,6 +367,7 @@ Tensor fused_moe_fused_experts(
     int64_t num_experts_per_tok, bool use_grouped_topk, int64_t num_expert_group, int64_t topk_group,
     const c10::optional<Tensor>& silu, const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0,
     bool save_mid_res) {
+  OpScope op_scope("fused_moe_fused_experts");
   reject_unused(output_sample, input_sample, num_select_experts, silu, sigmoid, m0, save_mid_res);
   (void)select_experts_middle;  // caller scratch of the reference kernels; not needed here
   (void)routing_weights_middle;
@@ -293,6 +395,7 @@ Tensor fused_moe_fused_experts_v2(
     int64_t num_experts_per_tok, bool use_grouped_topk, int64_t num_expert_group, int64_t topk_group,
     const c10::optional<Tensor>& silu, const c10::optional<Tensor>& sigmoid, const c10::optional<Tensor>& m0,
     bool save_mid_res) {
+  OpScope op_scope("fused_moe_fused_experts_v2");
   (void)gather_buffer;
   (void)scatter_buffer;
   return fused_moe_fused_experts(output, input, output_sample, input_sample, gate_weights, up_weights,
@@ -310,6 +413,7 @@ Tensor fused_moe_fused_experts_v2(
 Tensor fused_moe_grouped_topk(Tensor& topk_experts_res, Tensor& topk_weights_res_bf16, Tensor& left_bf16,
                               Tensor& right_bf16, Tensor& topk_weights_res, Tensor& left, Tensor& right,
                               Tensor& max, Tensor& matmul_res, Tensor& softmax_res) {
+  OpScope op_scope("fused_moe_grouped_topk");
   check_cuda_contig(topk_experts_res, "topk_experts_res");
   check_cuda_contig(topk_weights_res_bf16, "topk_weights_res_bf16");
   check_cuda_contig(left_bf16, "left_bf16");
@@ -348,6 +452,7 @@ Tensor fused_moe_grouped_topk(Tensor& topk_experts_res, Tensor& topk_weights_res
 // my_ops/NoauxTcTopk.cpp:9-67 - same checks, same order of arguments
 Tensor noaux_tc_topk(Tensor& values, Tensor& indices, const Tensor& scores, int64_t n_groups,
                      int64_t topk_groups, int64_t top_k) {
+  OpScope op_scope("noaux_tc_topk");
   check_cuda_contig(values, "values");
   check_cuda_contig(indices, "indices");
   check_cuda_contig(scores, "scores");
@@ -405,6 +510,7 @@ Tensor dense_mlp(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& 
 Tensor mlp_w8a16_dq_forward(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& down_weight,
                             Tensor& gate_scale, Tensor& up_scale, Tensor& down_scale, Tensor& output,
                             int64_t blocksize) {
+  OpScope op_scope("mlp_w8a16_dq_forward");
   return dense_mlp(input, gate_weight, up_weight, down_weight, gate_scale, up_scale, down_scale, output, blocksize,
                    B200MOE_ACT_W8A16);
 }
@@ -413,6 +519,7 @@ Tensor mlp_w8a16_dq_forward(Tensor& input, Tensor& gate_weight, Tensor& up_weigh
 Tensor mlp_w8a8_quant_forward(Tensor& input, Tensor& gate_weight, Tensor& up_weight, Tensor& down_weight,
                               Tensor& gate_scale, Tensor& up_scale, Tensor& down_scale, Tensor& output,
                               int64_t blocksize) {
+  OpScope op_scope("mlp_w8a8_quant_forward");
   return dense_mlp(input, gate_weight, up_weight, down_weight, gate_scale, up_scale, down_scale, output, blocksize,
                    B200MOE_ACT_W8A8);
 }
@@ -420,6 +527,7 @@ Tensor mlp_w8a8_quant_forward(Tensor& input, Tensor& gate_weight, Tensor& up_wei
 // my_ops/MmW8A16Dq.cpp:185-229: output[M,N] = input[M,K] . dequant(weight [N,K], scale)^T.  Runs on the FP8 tensor
 // cores (activations quantised per row per 128 columns), like the expert GEMMs.
 Tensor mm_w8a16_dq_forward(Tensor& input, Tensor& weight, Tensor& scale, Tensor& output, int64_t blocksize) {
+  OpScope op_scope("mm_w8a16_dq_forward");
   check_cuda_contig(input, "input");
   check_cuda_contig(weight, "weight");
   check_cuda_contig(scale, "scale");
@@ -455,6 +563,7 @@ Tensor mm_w8a16_dq_forward(Tensor& input, Tensor& weight, Tensor& scale, Tensor&
 Tensor scaled_mm_fp8(const Tensor& self, const Tensor& mat2, const Tensor& scale_a, const Tensor& scale_b,
                      const c10::optional<Tensor>& bias, const c10::optional<Tensor>& scale_result,
                      c10::optional<ScalarType> out_dtype, bool use_fast_accum) {
+  OpScope op_scope("_scaled_mm");
   (void)use_fast_accum;
   check_cuda_contig(self, "self");
   check_cuda_contig(mat2, "mat2");
@@ -492,6 +601,9 @@ Tensor b200_moe_status() {
 
 TORCH_LIBRARY(my_ops, m) {
   m.def("b200_moe_status", b200_moe_status);
+  m.def("enable_profile", enable_profile);
+  m.def("disable_profile", disable_profile);
+  m.def("b200_profile_summary", b200_profile_summary);
   m.def("_scaled_mm", scaled_mm_fp8);
   m.def("fused_moe_grouped_topk", fused_moe_grouped_topk);
   m.def("fused_moe_fused_experts", fused_moe_fused_experts);
